@@ -86,13 +86,17 @@ class PageLedger:
 
     ``window`` (tokens, or None): a group whose layers only ever read the last ``window`` keys
     gives pages back as soon as every position in them has fallen out of every future query's
-    sight; the page-table entry then goes stale and is never read again.
+    sight; the page-table entry then goes stale and is never read again.  ``chunk`` (tokens, or None): the
+    group's layers only read keys of the query's own block of ``chunk`` positions, so every page wholly before
+    the block of the next position goes back the same way.
     """
 
-    def __init__(self, n_pages: int, page_size: int, max_pages_per_slot: int, window: Optional[int] = None):
+    def __init__(self, n_pages: int, page_size: int, max_pages_per_slot: int, window: Optional[int] = None,
+                 chunk: Optional[int] = None):
         self.page_size = page_size
         self.max_pages_per_slot = max_pages_per_slot
         self.window = window
+        self.chunk = chunk
         self.pool = FreeList(n_pages, "page")
         self._pages: Dict[int, Dict[int, int]] = {}  # slot -> {logical page index -> physical page}
 
@@ -103,9 +107,11 @@ class PageLedger:
 
     def first_live_page(self, next_pos: int) -> int:
         """Logical index of the first page a query at position >= next_pos can still see."""
-        if self.window is None:
-            return 0
-        first_key = max(0, next_pos - self.window + 1)
+        first_key = 0
+        if self.window is not None:
+            first_key = max(first_key, next_pos - self.window + 1)
+        if self.chunk is not None:
+            first_key = max(first_key, next_pos - next_pos % self.chunk)
         return first_key // self.page_size
 
     def pages_needed(self, cur_len: int, new_len: int) -> int:
@@ -133,7 +139,7 @@ class PageLedger:
         return added
 
     def trim(self, slot: int, next_pos: int) -> List[int]:
-        """Give back pages no future query (position >= next_pos) can see.  Only a windowed
+        """Give back pages no future query (position >= next_pos) can see.  Only a windowed or chunked
         group ever returns any."""
         held = self._pages.get(slot)
         if held is None:

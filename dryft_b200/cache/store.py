@@ -31,11 +31,16 @@ from .slots import CacheError, FreeList, PageLedger, pages_for
 @dataclass(frozen=True)
 class KVNeed:
     """What an attention-like mixer asks of the cache: keys and values of this shape, all of
-    them (``window=None``) or the last ``window``."""
+    them (``window=None``) or the last ``window``.  ``v_head_dim``: the size of a value row where it differs from
+    a key row's ``head_dim`` (a key row may hold several score maps' keys).  ``chunk``: queries only see keys of
+    their own block of ``chunk`` positions (counted from position 0), so pages wholly before the block of the
+    next position are given back."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -61,13 +66,17 @@ class CacheEntry:
 
 class _KVGroup:
     def __init__(self, need: KVNeed, run_steps: List[int], n_pages: int, page_size: int, max_slots: int,
-                 max_pages_per_slot: int, dtype: torch.dtype, device: torch.device):
+                 max_pages_per_slot: int, dtype: torch.dtype, device: torch.device, trim: bool = True):
         self.need = need
         self.run_steps = run_steps
-        self.ledger = PageLedger(n_pages, page_size, max_pages_per_slot, need.window)
+        # ``trim`` is off when a run step that borrows this group's entries sees keys another way than the owners do:
+        # what the owners could give back, the borrower may still read
+        self.trims = trim and (need.window is not None or need.chunk is not None)
+        self.ledger = PageLedger(n_pages, page_size, max_pages_per_slot, need.window if trim else None,
+                                 need.chunk if trim else None)
         shape = (len(run_steps), n_pages, need.kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
         self.page_table_host = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32)
         self.page_table = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32, device=device)
         self.dirty: set = set()
@@ -77,7 +86,7 @@ class _KVGroup:
         self.staged: Optional[torch.cuda.Event] = None
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class SequenceCache:
@@ -134,7 +143,10 @@ class SequenceCache:
                     raise CacheError(f"run step {i}: state_need() must give a StateNeed or a mapping of names to StateNeed, "
                                      f"got {st!r}")
         for need, steps in by_need.items():
-            g = _KVGroup(need, steps, n_pages, page_size, max_slots, max_pages_per_slot, dtype, device)
+            # a borrower's own view of the keys (window, chunk) must be the owner's for pages to be given back early
+            same_view = all(needs[i][0] is None or (needs[i][0].window, needs[i][0].chunk) == (need.window, need.chunk)
+                            for i, src in enumerate(borrow) if src is not None and src in steps)
+            g = _KVGroup(need, steps, n_pages, page_size, max_slots, max_pages_per_slot, dtype, device, trim=same_view)
             for j, s in enumerate(steps):
                 self._entry_of[s] = (len(self._groups), j)
             self._groups.append(g)
@@ -266,7 +278,7 @@ class SequenceCache:
         the step itself) and let windowed groups drop pages that fell out of sight."""
         self.len_host[slot] += n
         for g in self._groups:
-            if g.need.window is not None:
+            if g.trims:
                 g.ledger.trim(slot, self.len_host[slot])
 
     def check(self) -> None:

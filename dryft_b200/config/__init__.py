@@ -2,6 +2,7 @@
 
 from .spec import ExtraPart, LayerSpec, ModelSpec, PartSpec, RunStep
 from .qwen3 import ConfigError, Qwen3Config
+from .tevovik import TevovikConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -15,10 +16,11 @@ from .registry import (
 from .presets import PRESETS, preset
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict)
+register_architecture("Tevovik", TevovikConfig.from_dict)
 
 __all__ = [
     "ExtraPart",
-    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "PRESETS", "Qwen3Config", "RunStep",
+    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "PRESETS", "Qwen3Config", "RunStep", "TevovikConfig",
     "architecture_of", "config_from_dict", "known_architectures", "load_config", "load_model_spec",
     "preset", "register_architecture", "unregister_architecture",
 ]

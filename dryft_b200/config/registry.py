@@ -1,5 +1,5 @@
-"""One registry from an architecture's name (``config.json["architectures"][0]``) to what
-builds it.  The reference never reads ``architectures``; it serves one pinned checkpoint
+"""One registry from an architecture's name (``config.json["architectures"][0]``, or the string
+``config.json["architecture"]`` of checkpoints that name a single one) to what builds it.  The reference never reads ``architectures``; it serves one pinned checkpoint
 (``engine/dryft_qwen3/config.py:55-70``).  Here the name picks the typed configuration,
 and the configuration yields the ``ModelSpec`` every other component works from.
 """
@@ -40,9 +40,12 @@ def known_architectures() -> list:
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     archs = raw.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise KeyError("config.json: 'architectures' is missing or empty; known: " + ", ".join(known_architectures()))
-    name = archs[0]
+    if isinstance(archs, (list, tuple)) and archs:
+        name = archs[0]
+    elif isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        name = raw["architecture"]
+    else:
+        raise KeyError("config.json: 'architectures' (or 'architecture') is missing or empty; known: " + ", ".join(known_architectures()))
     if name not in _ARCHITECTURES:
         raise KeyError(f"config.json: unknown architecture {name!r}; known: " + ", ".join(known_architectures()))
     return _ARCHITECTURES[name]

@@ -1,0 +1,208 @@
+// Mixture of experts: the router's choice and the experts evaluated assignment by assignment.
+//
+//   moe_route     scores s = softmax(logits) over all E experts (32-bit).  The experts form `n_groups` equal groups of
+//                 neighbours; a group scores its largest member; only experts of the `keep` best groups can be chosen
+//                 (n_groups = keep = 1: no groups).  The `top` allowed experts with the largest scores are chosen;
+//                 their weights are the scores themselves, or the scores divided by their sum (`renorm`).
+//                 Ties go to the lower index.  One warp per token.
+//   moe_rows      an assignment a = (token, k) multiplies its token's activation row by its expert's matrices, every
+//                 weight row read once per assignment (a matrix-vector product per warp row): the form for few
+//                 tokens (decode) and for the 32-bit path.
+//                   mode 0:  act[a, f] = silu(Wg_e[f] . h[token]) * (Wu_e[f] . h[token])      (W_gu [E, 2F, K]: gate rows, then up rows)
+//                   mode 1:  y[a, c]   = Wd_e[c] . act[a]                                    (W_d [E, C, F])
+//                 32-bit accumulation in a fixed order, one rounding to T at the end.
+//   moe_combine   out[n] = sum_k wts[n, k] * y[n*top + k]   (32-bit sum, rounded once) for callers that do not fold the
+//                 weighted sum into a kernel of their own.
+// No block waits on another block.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int ROUTE_WARPS = 4;
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
+    const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
+    int* __restrict__ idx_out, float* __restrict__ w_out) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * ROUTE_WARPS + warp;
+  if (n >= n_tokens) return;
+  float* s = sm + (size_t)warp * (E + n_groups);   // scores; an expert that may no longer be chosen is set to -1
+  float* gs = s + E;                               // group scores
+  const float* z = logits + (size_t)n * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(z[e] - mx);
+    s[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+  __syncwarp();
+  if (n_groups > 1) {
+    const int gsz = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float m = -1.f;
+      for (int j = 0; j < gsz; ++j) m = fmaxf(m, s[g * gsz + j]);
+      gs[g] = m;
+    }
+    __syncwarp();
+    // take the `keep` best groups away one by one (marking them -2); what is left at the end is shut out
+    for (int r = 0; r < keep; ++r) {
+      float bv = -1.5f;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (gs[g] > bv) { bv = gs[g]; bi = g; }
+      warp_argmax(bv, bi);
+      if (lane == 0 && bi < n_groups) gs[bi] = -2.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / gsz] != -2.f) s[e] = -1.f;
+    __syncwarp();
+  }
+  float wsum = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float bv = -2.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > bv) { bv = s[e]; bi = e; }
+    warp_argmax(bv, bi);
+    if (bi >= E) { bi = 0; bv = 0.f; }   // nothing comparable left (a NaN row): a defined choice of weight zero
+    if (bv < 0.f) bv = 0.f;              // fewer allowed experts than `top`
+    if (lane == 0) {
+      idx_out[(size_t)n * top + r] = bi;
+      w_out[(size_t)n * top + r] = bv;
+      s[bi] = -2.f;
+    }
+    wsum += bv;
+    __syncwarp();
+  }
+  if (renorm && lane == 0 && wsum > 0.f)
+    for (int r = 0; r < top; ++r) w_out[(size_t)n * top + r] /= wsum;
+}
+
+constexpr int ROWS_THREADS = 128;
+constexpr int ROWS_PER_BLOCK = 32;   // output features a block computes (8 per warp)
+
+template <typename T>
+__global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
+    const T* __restrict__ a_in, int a_div,              // activation row of assignment a: a_in[(a / a_div) * K]
+    const T* __restrict__ w, const int* __restrict__ idx, int E, int rows_per_expert, int K, int n_out, int mode,
+    T* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  T* xs = reinterpret_cast<T*>(smraw);
+  const int a = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int e = idx[a];
+  e = min(max(e, 0), E - 1);
+  const T* x = a_in + (size_t)(a / a_div) * K;
+  for (int c = threadIdx.x; c < K; c += ROWS_THREADS) xs[c] = x[c];
+  __syncthreads();
+  const T* we = w + (size_t)e * rows_per_expert * K;
+  const int o0 = blockIdx.y * ROWS_PER_BLOCK;
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = (K % V) == 0;
+  for (int o = o0 + warp; o < min(o0 + ROWS_PER_BLOCK, n_out); o += ROWS_THREADS / 32) {
+    float d0 = 0.f, d1 = 0.f;
+    const T* r0 = we + (size_t)o * K;
+    const T* r1 = we + (size_t)(n_out + o) * K;   // mode 0: the matching up row
+    if (vec) {
+      for (int c = lane * V; c < K; c += 32 * V) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xs + c);
+        const uint4 w0 = *reinterpret_cast<const uint4*>(r0 + c);
+        const T* xe = reinterpret_cast<const T*>(&xv);
+        const T* e0 = reinterpret_cast<const T*>(&w0);
+#pragma unroll
+        for (int t = 0; t < V; ++t) d0 = fmaf(to_f32<T>(e0[t]), to_f32<T>(xe[t]), d0);
+        if (mode == 0) {
+          const uint4 w1 = *reinterpret_cast<const uint4*>(r1 + c);
+          const T* e1 = reinterpret_cast<const T*>(&w1);
+#pragma unroll
+          for (int t = 0; t < V; ++t) d1 = fmaf(to_f32<T>(e1[t]), to_f32<T>(xe[t]), d1);
+        }
+      }
+    } else {
+      for (int c = lane; c < K; c += 32) {
+        const float xv = to_f32<T>(xs[c]);
+        d0 = fmaf(to_f32<T>(r0[c]), xv, d0);
+        if (mode == 0) d1 = fmaf(to_f32<T>(r1[c]), xv, d1);
+      }
+    }
+    d0 = warp_sum(d0);
+    if (mode == 0) {
+      d1 = warp_sum(d1);
+      d0 = d0 / (1.f + expf(-d0)) * d1;
+    }
+    if (lane == 0) out[(size_t)a * n_out + o] = from_f32<T>(d0);
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ wts, int top, int width, T* __restrict__ out) {
+  const int n = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v = fmaf(wts[(size_t)n * top + k], to_f32<T>(y[((size_t)n * top + k) * width + c]), v);
+    out[(size_t)n * width + c] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+int rows_launch(const void* a_in, int a_div, const void* w, const int* idx, int E, int K, int n_out, int mode, void* out,
+                int n_assign, cudaStream_t st) {
+  if (n_assign <= 0) return 0;
+  if (E < 1 || K < 1 || n_out < 1 || a_div < 1 || (mode != 0 && mode != 1)) return DRYFT_ERR_UNSUPPORTED;
+  const size_t smem = (sizeof(T) * (size_t)K + 15) / 16 * 16;
+  if (smem > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int tiles = (n_out + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+  if (tiles > 65535) return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid(n_assign, tiles);
+  moe_rows_kernel<T><<<grid, ROWS_THREADS, smem, st>>>((const T*)a_in, a_div, (const T*)w, idx, E, mode == 0 ? 2 * n_out : n_out, K,
+                                                      n_out, mode, (T*)out);
+  return launch_status();
+}
+}  // namespace
+
+DRYFT_API int dryft_moe_route(const float* logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
+                              int* idx_out, float* w_out, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups) return DRYFT_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(float) * (size_t)ROUTE_WARPS * (E + n_groups);
+  if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  moe_route_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, smem, st>>>(logits, n_tokens, E, n_groups, keep,
+                                                                                               top, renorm, idx_out, w_out);
+  return launch_status();
+}
+
+DRYFT_API int dryft_moe_rows(int is_bf16, const void* a_in, int a_div, const void* w, const int* idx, int E, int K, int n_out,
+                             int mode, void* out, int n_assign, cudaStream_t st) {
+  return is_bf16 ? rows_launch<__nv_bfloat16>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, st)
+                 : rows_launch<float>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, st);
+}
+
+DRYFT_API int dryft_moe_combine(int is_bf16, const void* y, const float* wts, int top, int width, void* out, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (is_bf16)
+    moe_combine_kernel<__nv_bfloat16><<<n, 256, 0, st>>>((const __nv_bfloat16*)y, wts, top, width, (__nv_bfloat16*)out);
+  else
+    moe_combine_kernel<float><<<n, 256, 0, st>>>((const float*)y, wts, top, width, (float*)out);
+  return launch_status();
+}

@@ -71,7 +71,12 @@ class DecoderModel:
         """Run the step's tokens through every run step; logits ``[n_want, vocab]`` float32 at the
         packed rows ``want_rows`` (None if nothing is wanted).  ``all_rows`` says that ``want_rows`` is simply
         every row in order (a decode step), which lets the head take the fused path."""
-        res = Residual(self.embedding.forward(ctx.tokens, ctx.n_tokens))
+        if getattr(self.embedding, "takes_context", False):   # an embedding that adds the tokens' positions
+            res = self.embedding.forward(ctx.tokens, ctx.n_tokens, ctx)
+        else:
+            res = self.embedding.forward(ctx.tokens, ctx.n_tokens)
+        if not isinstance(res, Residual):
+            res = Residual(res)
         sched = self.spec.schedule
         for i, st in enumerate(sched):
             block = self.blocks[st.layer]

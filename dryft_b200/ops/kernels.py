@@ -22,7 +22,7 @@ from . import build
 
 _i, _f, _p, _ll, _ull = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_ulonglong
 
-CORE_SOURCES = ("elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "sample.cu", "gemm_small_m.cu")
+CORE_SOURCES = ("elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "sample.cu", "gemm_small_m.cu", "stream32.cu", "kv_maps.cu", "moe.cu")
 UNSUPPORTED = -2
 
 
@@ -64,9 +64,18 @@ def core() -> ctypes.CDLL:
             lib.dryft_sample_rows.argtypes = [_p, _i, _i, _ll, _f, _i, _ull, _p, _p, _i, _p, _p, _p, _p]
             lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
             lib.dryft_row_sumsq.argtypes = [_p, _i, _i, _p, _p, _p, _p]
+            lib.dryft_embed_sinusoid.argtypes = [_i, _i, _p, _p, _p, _p, _f, _p, _p, _i, _i, _i, _p, _p]
+            lib.dryft_stream_norm_add.argtypes = [_i, _p, _p, _i, _p, _f, _f, _p, _p, _i, _i, _p]
+            lib.dryft_stream_norm_rows.argtypes = [_i, _i, _p, _p, _p, _f, _f, _p, _i, _i, _p]
+            lib.dryft_kv_maps_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
+            lib.dryft_moe_route.argtypes = [_p, _i, _i, _i, _i, _i, _i, _p, _p, _p]
+            lib.dryft_moe_rows.argtypes = [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _p]
+            lib.dryft_moe_combine.argtypes = [_i, _p, _p, _i, _i, _p, _i, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
                          "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store", "dryft_rope_table",
-                         "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq"):
+                         "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq",
+                         "dryft_embed_sinusoid", "dryft_stream_norm_add", "dryft_stream_norm_rows", "dryft_kv_maps_store",
+                         "dryft_moe_route", "dryft_moe_rows", "dryft_moe_combine"):
                 getattr(lib, name).restype = _i
             _core = lib
         return _core
@@ -90,6 +99,29 @@ def attention_rows_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
             lib.dryft_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _f, _i, _p]
             lib.dryft_attn_rows.restype = _i
             if (lib.dryft_attn_rows_head_dim(), lib.dryft_attn_rows_group(), lib.dryft_attn_rows_page()) != (head_dim, group, page):
+                raise KernelError(f"{path} was compiled for other sizes")
+            _variants[key] = lib
+        return lib
+
+
+def diff_attention_rows_lib(qk_dim: int, v_dim: int, group: int, page: int) -> ctypes.CDLL:
+    """The row-wise (decode / 32-bit) differential attention kernel compiled for these sizes."""
+    if qk_dim <= 0 or v_dim <= 0 or 2 * qk_dim > 512 or v_dim > 512:
+        raise KernelError(f"differential attention takes map sizes up to 256 and value sizes up to 512, got {qk_dim}, {v_dim}")
+    if group < 1 or group > 8:
+        raise KernelError(f"differential attention takes 1..8 query heads per kv head, got {group}")
+    key = ("diff_rows", qk_dim, v_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("diff_attn_rows", ("diff_attn_rows.cu",),
+                                       {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_diff_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _f, _i, _i, _f, _f,
+                                                 _f, _p]
+            lib.dryft_diff_attn_rows.restype = _i
+            if (lib.dryft_diff_attn_rows_qk_dim(), lib.dryft_diff_attn_rows_v_dim(), lib.dryft_diff_attn_rows_group(),
+                    lib.dryft_diff_attn_rows_page()) != (qk_dim, v_dim, group, page):
                 raise KernelError(f"{path} was compiled for other sizes")
             _variants[key] = lib
         return lib
@@ -572,6 +604,189 @@ def attn_prefill_tc(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_s
                                   k_pages.shape[0], n_heads, n_kv, float(scale), int(window or 0),
                                   _ptr(error_flag(q.device)), _stream()),
         f"attn_prefill_tc (head_dim {head_dim})")
+
+
+# ----------------------------------------------------------------------------- 32-bit residual stream
+def embed_sinusoid(tokens, tok_pos, table, freq, scale: float, x32, h=None, err=None) -> None:
+    """``x32[n] = table[tokens[n]] * scale + s(tok_pos[n])`` with ``s[2i] = sin(pos * freq[i])``, ``s[2i+1] = cos`` of the
+    same angle; ``h`` (optional, bfloat16 or float32) receives the row rounded to its type."""
+    n, width = x32.shape
+    _need(tokens, "tokens", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32)
+    _need(table, "embedding table", None, (None, width))
+    _need(freq, "freq", torch.float32, ((width + 1) // 2,))
+    _need(x32, "stream", torch.float32)
+    if tokens.numel() < n or tok_pos.numel() < n:
+        raise KernelError("embed_sinusoid: fewer tokens than rows")
+    if h is not None:
+        _need(h, "h", None, (n, width))
+    if err is not None:
+        _need(err, "err", torch.int32)
+    _ok(core().dryft_embed_sinusoid(_act(table, "embedding table"), _act(h, "h") if h is not None else 0, _ptr(tokens), _ptr(tok_pos),
+                                    _ptr(table), _ptr(freq), float(scale), _ptr(x32), _ptr(h), n, width, table.shape[0], _ptr(err),
+                                    _stream()), "embed_sinusoid")
+
+
+def stream_norm_add(y, weight, offset: float, eps: float, x32, h=None, wts=None, top: int = 0) -> None:
+    """``x32[n] += y[n] / sqrt(mean(y[n]^2) + eps) * (offset + weight)`` in 32-bit; ``h`` (optional, of ``y``'s type) receives
+    the new row rounded.  With ``wts`` ``[n, top]`` float32, ``y`` is ``[n * top, width]`` and row ``n`` is the weighted sum
+    ``sum_k wts[n, k] * y[n * top + k]`` (formed in 32-bit)."""
+    n, width = x32.shape
+    _need(x32, "stream", torch.float32)
+    _need(weight, "norm weight", torch.float32, (width,))
+    if wts is not None:
+        if top <= 0:
+            raise KernelError("stream_norm_add: wts needs top > 0")
+        _need(wts, "wts", torch.float32, (n, top))
+        _need(y, "y", None, (n * top, width))
+    else:
+        top = 0
+        _need(y, "y", None, (n, width))
+    if h is not None:
+        _need(h, "h", y.dtype, (n, width))
+    _ok(core().dryft_stream_norm_add(_act(y, "y"), _ptr(y), _ptr(wts), int(top), _ptr(weight), float(offset), float(eps), _ptr(x32),
+                                     _ptr(h), n, width, _stream()), f"stream_norm_add (width {width})")
+
+
+def stream_norm_rows(x, weight, offset: float, eps: float, out, rows=None) -> None:
+    """``out[r] = norm(x[src]) * (offset + weight)`` with ``src = rows[r]`` if rows is given; ``x`` and ``out`` are float32 or
+    bfloat16 independently."""
+    width = x.shape[-1]
+    _need(x, "x")
+    _need(weight, "norm weight", torch.float32, (width,))
+    n = out.shape[0]
+    _need(out, "norm output", None, (n, width))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n:
+            raise KernelError("stream_norm_rows: fewer row indices than output rows")
+    elif x.shape[0] < n:
+        raise KernelError("stream_norm_rows: input has fewer rows than the output")
+    _ok(core().dryft_stream_norm_rows(_act(x, "x"), _act(out, "out"), _ptr(x), _ptr(rows), _ptr(weight), float(offset), float(eps),
+                                      _ptr(out), n, width, _stream()), f"stream_norm_rows (width {width})")
+
+
+# ----------------------------------------------------------------------------- differential attention
+def kv_maps_store(proj, q_norm_w, k_norm_w, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table, n_heads: int,
+                  n_kv_heads: int, maps: int, dim: int, v_dim: int, eps: float, write_kv: bool = True) -> None:
+    """Rows of ``proj`` are ``[q: heads x maps x dim | k: kv_heads x maps x dim | v: kv_heads x v_dim | ...]`` (k and v absent
+    without ``write_kv``).  Every (head, map) vector of q and k gets its RMS norm (weights ``[dim]``, optional); q goes to
+    ``q_out [n, heads, maps*dim]``, k and v into the paged cache at each token's (slot, position)."""
+    n = proj.shape[0]
+    need_w = n_heads * maps * dim + ((n_kv_heads * maps * dim + n_kv_heads * v_dim) if write_kv else 0)
+    _need(proj, "proj")
+    if proj.dim() != 2 or proj.shape[1] < need_w:
+        raise KernelError(f"kv_maps_store: projection rows have {tuple(proj.shape)}, need at least {need_w} columns")
+    is_bf16 = _act(proj, "proj")
+    for w_, nm in ((q_norm_w, "q norm weight"), (k_norm_w, "k norm weight")):
+        if w_ is not None:
+            _need(w_, nm, torch.float32, (dim,))
+    _need(tok_slot, "tok_slot", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32)
+    if tok_slot.numel() < n or tok_pos.numel() < n:
+        raise KernelError("kv_maps_store: token index arrays shorter than the batch")
+    _need(q_out, "q_out", proj.dtype, (n, n_heads, maps * dim))
+    page_size = max_pages = 0
+    if write_kv:
+        _need(k_pages, "k_pages", proj.dtype, (None, n_kv_heads, None, maps * dim))
+        _need(v_pages, "v_pages", proj.dtype, (k_pages.shape[0], n_kv_heads, k_pages.shape[2], v_dim))
+        _need(page_table, "page_table", torch.int32)
+        page_size, max_pages = k_pages.shape[2], page_table.shape[1]
+    _ok(core().dryft_kv_maps_store(is_bf16, _ptr(proj), proj.shape[1], _ptr(q_norm_w), _ptr(k_norm_w), _ptr(tok_slot), _ptr(tok_pos),
+                                   _ptr(q_out), _ptr(k_pages if write_kv else None), _ptr(v_pages if write_kv else None),
+                                   _ptr(page_table if write_kv else None), max_pages, n, n_heads, n_kv_heads, maps, dim, v_dim,
+                                   page_size, float(eps), int(write_kv), _stream()), "kv_maps_store")
+
+
+def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: float, lam: float, sub_eps: float,
+                   out_scale: float, window: Optional[int] = None, chunk: Optional[int] = None, gate=None, gate_col: int = 0,
+                   n_splits: int = 1, part_o=None, part_ml=None) -> None:
+    """Differential attention of independent rows: ``q [n, heads, 2*dim]`` (normalised), keys ``[pages, kv, page, 2*dim]``,
+    values ``[pages, kv, page, v_dim]``; ``out [n, heads*v_dim] = gate * out_scale * unit_rms(a1 - lam * a2)``.  ``gate``: a
+    2-D tensor whose columns ``gate_col .. gate_col + heads - 1`` hold one logit per head (sigmoid is applied)."""
+    n, n_heads, kw = q.shape
+    is_bf16 = _act(q, "q")
+    _need(q, "q")
+    n_kv, page, v_dim = k_pages.shape[1], k_pages.shape[2], v_pages.shape[3]
+    _need(k_pages, "k_pages", q.dtype, (None, n_kv, page, kw))
+    _need(v_pages, "v_pages", q.dtype, (k_pages.shape[0], n_kv, page, v_dim))
+    for t, nm in ((page_table, "page_table"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if tok_slot.numel() < n or tok_pos.numel() < n:
+        raise KernelError("diff_attn_rows: token index arrays shorter than the batch")
+    _need(out, "attention output", q.dtype, (n, n_heads * v_dim))
+    if n_heads % n_kv or kw % 2:
+        raise KernelError(f"diff_attn_rows: {n_heads} query heads / {n_kv} kv heads / key rows of {kw}")
+    gate_ptr, gate_stride = None, 0
+    if gate is not None:
+        _need(gate, "gate", q.dtype)
+        if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+            raise KernelError("diff_attn_rows: gate columns outside the gate tensor")
+        gate_ptr, gate_stride = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    if n_splits > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < n * n_heads * 2 * n_splits * v_dim or part_ml.numel() < n * n_heads * 2 * n_splits * 2:
+            raise KernelError("diff_attn_rows: partial buffers too small for the split count")
+    lib = diff_attention_rows_lib(kw // 2, v_dim, n_heads // n_kv, page)
+    _ok(lib.dryft_diff_attn_rows(is_bf16, _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(tok_slot),
+                                 _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, n_splits,
+                                 float(scale), int(window or 0), int(chunk or 0), float(lam), float(sub_eps), float(out_scale),
+                                 _stream()), f"diff_attn_rows (dims {kw // 2}, {v_dim})", n_kernels=2 if n_splits > 1 else 1)
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False) -> None:
+    """The router's choice per token from 32-bit ``logits [n, experts]``: ``idx_out [n, top]`` int32, ``w_out [n, top]`` float32."""
+    n, e = logits.shape
+    _need(logits, "router logits", torch.float32)
+    _need(idx_out, "idx_out", torch.int32, (n, top))
+    _need(w_out, "w_out", torch.float32, (n, top))
+    _ok(core().dryft_moe_route(_ptr(logits), n, e, int(n_groups), int(keep), int(top), int(renorm), _ptr(idx_out), _ptr(w_out),
+                               _stream()), f"moe_route ({e} experts, {n_groups} groups, keep {keep}, top {top})")
+
+
+def moe_rows(a, w, idx, out, mode: str) -> None:
+    """Experts evaluated assignment by assignment.  ``idx [n, top]`` int32 names each assignment's expert.
+    ``mode="gate_up"``: ``a [n, K]`` token rows, ``w [E, 2F, K]``, ``out [n*top, F] = silu(gate) * up``;
+    ``mode="down"``: ``a [n*top, F]``, ``w [E, C, F]``, ``out [n*top, C]``."""
+    n_assign = idx.numel()
+    _need(idx, "idx", torch.int32)
+    is_bf16 = _act(a, "a")
+    _need(a, "a")
+    _need(w, "w", a.dtype)
+    e, r, k = w.shape
+    if mode == "gate_up":
+        top = idx.shape[1]
+        n_out, code, a_div = r // 2, 0, top
+        if a.shape != (idx.shape[0], k) or r % 2:
+            raise KernelError(f"moe_rows: activations {tuple(a.shape)} against weights {tuple(w.shape)}")
+    elif mode == "down":
+        n_out, code, a_div = r, 1, 1
+        if a.shape != (n_assign, k):
+            raise KernelError(f"moe_rows: activations {tuple(a.shape)} against weights {tuple(w.shape)}")
+    else:
+        raise KernelError(f"moe_rows: unknown mode {mode!r}")
+    _need(out, "out", a.dtype, (n_assign, n_out))
+    _ok(core().dryft_moe_rows(is_bf16, _ptr(a), a_div, _ptr(w), _ptr(idx), e, k, n_out, code, _ptr(out), n_assign, _stream()),
+        f"moe_rows ({mode}, K={k}, out={n_out})")
+
+
+def moe_combine(y, wts, out) -> None:
+    """``out[n] = sum_k wts[n, k] * y[n * top + k]``."""
+    n, top = wts.shape
+    _need(wts, "wts", torch.float32)
+    _need(y, "y", None, (n * top, out.shape[1]))
+    _need(out, "out", y.dtype, (n, y.shape[1]))
+    _ok(core().dryft_moe_combine(_act(y, "y"), _ptr(y), _ptr(wts), top, y.shape[1], _ptr(out), n, _stream()), "moe_combine")
+
+
+def diff_attention_prefill_supported(qk_dim: int, v_dim: int, group: int, page: int) -> bool:
+    return False
+
+
+def moe_grouped_supported(hidden: int, inter: int) -> bool:
+    return False
 
 
 # ----------------------------------------------------------------------------- matrix products

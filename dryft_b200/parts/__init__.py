@@ -6,7 +6,7 @@ from .base import (
     BLOCKS, EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, POSITIONS, Registry, Residual, Runtime, StepContext, TensorInfo,
     register_block, register_embedding, register_ffn, register_head, register_mixer, register_norm, register_position,
 )
-from . import attention, block, embedding, ffn, norm, position  # noqa: F401  (registration)
+from . import attention, block, diff_attention, embedding, ffn, moe, norm, position  # noqa: F401  (registration)
 from .linear import linear
 
 __all__ = [

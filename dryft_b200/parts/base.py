@@ -100,6 +100,9 @@ class Residual:
     # product for the product behind that norm, which then has no prologue (it scales its sums instead)
     xw: Optional[torch.Tensor] = None
     xw_norm: Optional[Any] = None
+    # a stream kept in 32-bit whatever the activation type (``x`` is float32): ``h`` is ``x`` rounded to the activation
+    # type, what the next sublayer reads (``x`` itself in the 32-bit path)
+    h: Optional[torch.Tensor] = None
 
 
 def fused_rms(norm) -> Optional[Tuple[torch.Tensor, float]]:

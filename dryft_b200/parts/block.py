@@ -79,3 +79,45 @@ class PreNormBlock:
             return Residual(x, a)
         h = self.norm_ffn.add_forward(x, a)
         return Residual(x, self.ffn.forward(h, ctx))
+
+
+@register_block("outnorm")
+class OutNormBlock:
+    """The norm on each sublayer's output only, around a 32-bit stream:
+
+        x += norm_mixer(mixer(h))      h = x rounded to the activation type (the sublayers read the stream itself)
+        x += norm_ffn(ffn(h))
+
+    ``res.x`` is float32 in both precisions; each norm-and-add is one kernel that also leaves the rounded stream for
+    the next sublayer (``csrc/stream32.cu``).  The norms must offer ``add_into`` (``rmsnorm_offset`` does).  A
+    feed-forward that offers ``forward_parts`` (a routed one: ``top`` rows per token and their weights) has its
+    weighted sum formed inside that kernel.  A layer without a feed-forward stops after the mixer."""
+
+    def __init__(self, norm_mixer, mixer, norm_ffn, ffn):
+        for nm in (norm_mixer, norm_ffn):
+            if nm is not None and not hasattr(nm, "add_into"):
+                raise ValueError("the 'outnorm' arrangement needs norms that offer add_into (a 32-bit stream)")
+        self.norm_mixer = norm_mixer
+        self.mixer = mixer
+        self.norm_ffn = norm_ffn
+        self.ffn = ffn
+
+    def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True) -> Residual:
+        x = res.x
+        if x.dtype != torch.float32:
+            raise ValueError("the 'outnorm' arrangement keeps its stream in float32; the embedding must start one")
+        if res.delta is not None:
+            x.add_(res.delta)
+        act = self.mixer.rt.dtype
+        h = res.h if res.h is not None else (x if act == torch.float32 else x.to(act))
+        a = self.mixer.forward(h, ctx, cache, state, owns_cache)
+        h = self.norm_mixer.add_into(x, a)
+        if self.ffn is None:
+            return Residual(x, h=h)
+        parts = getattr(self.ffn, "forward_parts", None)
+        if parts is not None:
+            y, wts, top = parts(h, ctx)
+            h = self.norm_ffn.add_into(x, y, wts=wts, top=top)
+        else:
+            h = self.norm_ffn.add_into(x, self.ffn.forward(h, ctx))
+        return Residual(x, h=h)

@@ -12,7 +12,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..ops import kernels as K
-from .base import Runtime, TensorInfo, fused_rms, register_embedding, register_head
+from .base import Residual, Runtime, StepContext, TensorInfo, fused_rms, register_embedding, register_head
 from .linear import fusable_rows, linear
 
 
@@ -39,18 +39,53 @@ class Embedding:
         return out if out.dtype == self.rt.dtype else out.to(self.rt.dtype)
 
 
+@register_embedding("sinusoid_embedding")
+class SinusoidEmbedding:
+    """``x = table[id] * scale + s(p)``: the token's row times a constant, plus a sinusoidal vector of the token's
+    position ``p`` in its sequence, ``s[2i] = sin(p * base^(-2i/W))`` and ``s[2i+1] = cos`` of the same angle.  The
+    frequencies are evaluated on the host in 64-bit and rounded once; angles, sines and the sum are 32-bit
+    (``csrc/stream32.cu``).  It starts a 32-bit residual stream: the result is a ``Residual`` whose ``x`` is float32 and
+    whose ``h`` is the same rows in the activation type (the stream itself in the 32-bit path).  ``params["name"]`` is
+    the table's tensor name behind the prefix (default ``weight``)."""
+
+    takes_context = True   # forward needs the step's token positions
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        return {prefix + params.get("name", "weight"): TensorInfo((params["vocab_size"], params["hidden_size"]), "table")}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
+        base = float(params.get("base", 10000.0))
+        self.table = weights.load(prefix + params.get("name", "weight"), "table")
+        half = (self.hidden + 1) // 2
+        freq = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / self.hidden)
+        self.freq = freq.to(torch.float32).to(rt.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        K.watch_flag(self.err, "a token id outside the embedding table reached the embedding gather (its row was zeroed)")
+
+    def forward(self, tokens: torch.Tensor, n_rows: int, ctx: StepContext) -> Residual:
+        x = torch.empty((n_rows, self.hidden), dtype=torch.float32, device=self.table.device)
+        h = None if self.rt.dtype == torch.float32 else torch.empty((n_rows, self.hidden), dtype=self.rt.dtype, device=x.device)
+        K.embed_sinusoid(tokens, ctx.tok_pos, self.table, self.freq, self.scale, x, h, self.err)
+        return Residual(x, h=x if h is None else h)
+
+
 @register_head("lm_head")
 class LMHead:
     @staticmethod
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
-        return {prefix + "weight": TensorInfo((params["vocab_size"], params["hidden_size"]), "matrix",
-                                        optional=bool(params["tied"]))}
+        return {prefix + params.get("name", "weight"): TensorInfo((params["vocab_size"], params["hidden_size"]), "matrix",
+                                                                  optional=bool(params["tied"]))}
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime, embedding: Optional[Embedding] = None):
         self.rt = rt
         self.vocab = int(params["vocab_size"])
         self.tied = bool(params["tied"])
-        name = prefix + "weight"
+        name = prefix + params.get("name", "weight")   # the tensor's name behind the prefix
         if self.tied:
             if embedding is None:
                 raise ValueError("a tied output head needs the embedding it is tied to")

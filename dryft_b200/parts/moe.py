@@ -1,0 +1,106 @@
+"""Mixture-of-experts feed-forward with group-limited top-k routing.
+
+``E`` small SwiGLU experts (``down(silu(gate(h)) * up(h))``, no biases); a token uses ``top`` of them.  Router:
+``z = W_router h`` and ``s = softmax(z)`` over all experts in 32-bit; the experts form ``groups`` equal groups of
+neighbours, a group scores its largest member, and only experts of the ``keep`` best groups can be chosen; the ``top``
+largest scores among those are the token's experts, weighted by their scores ``s`` as they are (or divided by their sum
+with ``renormalize``).  The output is the weighted sum of the chosen experts' outputs.
+
+The router's product runs in 32-bit on the activations as the layer hands them over (``csrc/gemm_f32.cu``); the choice
+is ``csrc/moe.cu:moe_route``.  The experts run assignment by assignment for few tokens and in the 32-bit path
+(``csrc/moe.cu:moe_rows``: every chosen expert's weights are read once per assignment), and as grouped tensor-core
+products over the tokens sorted by expert for prompts in bfloat16 (``csrc/moe_grouped.cu``).  The weighted sum is left
+to the caller through ``forward_parts`` (a layer that normalises the sum forms it inside its norm kernel in 32-bit);
+``forward`` forms it itself.  ``params["names"]`` maps roles to tensor names behind the prefix.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Tuple
+
+import torch
+
+from ..ops import kernels as K
+from .base import Runtime, StepContext, TensorInfo, register_ffn
+
+_ROLES = {"router": "router.weight", "expert": "experts.{}.", "gate": "gate_proj.weight", "up": "up_proj.weight",
+          "down": "down_proj.weight"}
+
+
+def _names(params: Mapping) -> Dict[str, str]:
+    given = params.get("names") or {}
+    return {role: given.get(role, default) for role, default in _ROLES.items()}
+
+
+@register_ffn("moe")
+class MoE:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        w, f, e = params["hidden_size"], params["intermediate_size"], params["experts"]
+        nm = _names(params)
+        t = {prefix + nm["router"]: TensorInfo((e, w), "matrix")}
+        for i in range(e):
+            ep = prefix + nm["expert"].format(i)
+            t[ep + nm["gate"]] = TensorInfo((f, w), "matrix")
+            t[ep + nm["up"]] = TensorInfo((f, w), "matrix")
+            t[ep + nm["down"]] = TensorInfo((w, f), "matrix")
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.groups = int(params.get("groups", 1))
+        self.keep = int(params.get("keep", self.groups))
+        self.renorm = bool(params.get("renormalize", False))
+        if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
+            raise ValueError(f"moe: {self.experts} experts, {self.groups} groups, keep {self.keep}, top {self.top} do not go together")
+        nm = _names(params)
+        # the router always runs in 32-bit: its weight is widened once here
+        self.w_router = weights.load(prefix + nm["router"], "matrix").to(torch.float32).contiguous()
+        gu, dn = [], []
+        for i in range(self.experts):
+            ep = prefix + nm["expert"].format(i)
+            gu += [ep + nm["gate"], ep + nm["up"]]
+            dn.append(ep + nm["down"])
+        # [E, 2F, W] (an expert's gate rows, then its up rows) and [E, W, F]
+        self.w_gate_up = weights.load_fused(gu, [self.inter] * len(gu), self.hidden).view(self.experts, 2 * self.inter, self.hidden)
+        self.w_down = weights.load_fused(dn, [self.hidden] * len(dn), self.inter).view(self.experts, self.hidden, self.inter)
+        self.use_grouped = (rt.is_bf16 and self.w_gate_up.dtype == torch.bfloat16
+                            and K.moe_grouped_supported(self.hidden, self.inter))
+        if self.use_grouped:
+            K.moe_grouped_lib()
+
+    GROUPED_MIN_TOKENS = 32   # below this every assignment streams its expert's weights itself
+
+    def route(self, h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Chosen experts ``[n, top]`` int32 and their weights ``[n, top]`` float32."""
+        n = h.shape[0]
+        logits = torch.empty((n, self.experts), dtype=torch.float32, device=h.device)
+        K.gemm_nt_f32(h if h.dtype == torch.float32 else h.to(torch.float32), self.w_router, logits)
+        idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
+        wts = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
+        K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)
+        return idx, wts
+
+    def forward_parts(self, h: torch.Tensor, ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        """``(y [n*top, hidden], wts [n, top], top)``: row ``n*top + k`` is the output of token ``n``'s k-th expert, not yet
+        weighted."""
+        n = h.shape[0]
+        idx, wts = self.route(h)
+        y = torch.empty((n * self.top, self.hidden), dtype=h.dtype, device=h.device)
+        if self.use_grouped and n >= self.GROUPED_MIN_TOKENS:
+            K.moe_grouped(h, self.w_gate_up, self.w_down, idx, y)
+        else:
+            act = torch.empty((n * self.top, self.inter), dtype=h.dtype, device=h.device)
+            K.moe_rows(h, self.w_gate_up, idx, act, "gate_up")
+            K.moe_rows(act, self.w_down, idx, y, "down")
+        return y, wts, self.top
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        y, wts, top = self.forward_parts(h, ctx)
+        out = torch.empty((h.shape[0], self.hidden), dtype=h.dtype, device=h.device)
+        K.moe_combine(y, wts, out)
+        return out

@@ -44,3 +44,46 @@ class RMSNorm:
         out = torch.empty((n, self.size), dtype=x.dtype, device=x.device)
         K.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows, x_out=None if rows is not None else x)
         return out
+
+
+@register_norm("rmsnorm_offset")
+class OffsetRMSNorm:
+    """``x / sqrt(mean(x^2) + eps) * (offset + w)``, all of it in 32-bit and rounded once: the norm with a weight
+    stored around zero (``offset = 1``).  Its input may be a 32-bit stream while the output has the activation type.
+    It does not offer ``rms_params`` (its arithmetic is not the one the decode products fold into themselves).
+    ``add_into`` is the form a layer with the norm on the sublayer's *output* uses: ``x32 += norm(y)``.
+    ``params["name"]`` is the weight's tensor name behind the prefix (default ``weight``)."""
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        return {prefix + params.get("name", "weight"): TensorInfo((params["size"],), "vector")}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.offset = float(params.get("offset", 1.0))
+        self.rt = rt
+        self.weight = weights.load(prefix + params.get("name", "weight"), "vector")  # float32 [size]
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+        n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+        out = torch.empty((n, self.size), dtype=self.rt.dtype, device=x.device)
+        K.stream_norm_rows(x, self.weight, self.offset, self.eps, out, rows=rows)
+        return out
+
+    def add_forward(self, x: torch.Tensor, delta: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                    n_rows: Optional[int] = None) -> torch.Tensor:
+        """``x += delta`` (in place, whatever ``rows`` says) and the norm of the sum: the pre-norm arrangement's use."""
+        K.residual_add(x, delta)
+        return self.forward(x, rows, n_rows)
+
+    def add_into(self, x32: torch.Tensor, y: torch.Tensor, want_h: bool = True, wts: Optional[torch.Tensor] = None,
+                 top: int = 0) -> Optional[torch.Tensor]:
+        """``x32 += norm(y)`` in place (``y``: a sublayer's output in the activation type; with ``wts [n, top]`` the
+        weighted sum of ``top`` rows of ``y`` per row of the stream).  Returns the new stream rounded to the
+        activation type (the stream itself in the 32-bit path), or None if ``want_h`` is off."""
+        h = None
+        if want_h and y.dtype != torch.float32:
+            h = torch.empty(x32.shape, dtype=y.dtype, device=x32.device)
+        K.stream_norm_add(y, self.weight, self.offset, self.eps, x32, h, wts=wts, top=top)
+        return (x32 if y.dtype == torch.float32 else h) if want_h else None
