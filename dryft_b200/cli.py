@@ -67,7 +67,7 @@ def cmd_generate(args) -> int:
     rng = random.Random(args.seed)
     for w in args.workload:
         _, b, inp, _ = _workload(w)
-        prompts += [[rng.randrange(eng.config.vocab_size) for _ in range(inp)] for _ in range(b)]
+        prompts += [[rng.randrange(eng.spec.vocab_size) for _ in range(inp)] for _ in range(b)]
     if not prompts:
         raise SystemExit("nothing to generate from: give --prompt-ids or --workload")
     if args.max_new_tokens is not None:
@@ -92,7 +92,7 @@ def cmd_bench(args) -> int:
         name, b, inp, out = _workload(w)
         totals, ttfts = [], []
         for s in range(args.samples + 1):  # the first sample is the warm-up
-            ids = [[rng.randrange(eng.config.vocab_size) for _ in range(inp)] for _ in range(b)]
+            ids = [[rng.randrange(eng.spec.vocab_size) for _ in range(inp)] for _ in range(b)]
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             ttft = None

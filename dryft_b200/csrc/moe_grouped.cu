@@ -1,0 +1,235 @@
+// Mixture of experts for many tokens (bfloat16): the assignments (token, k) sorted by expert, and the experts' two
+// products as grouped tensor-core products over the sorted rows.  Everything is decided on the device: no count ever
+// reaches the host, so a step with these launches can be captured in a graph.
+//
+//   moe_sort       counts per expert -> offsets[E+1]; perm[p] = assignment at sorted place p (the order inside an expert
+//                  is arbitrary: every row is computed on its own, so no result depends on it); the list of row tiles
+//                  (expert, first sorted place) that the products walk, and their number.  One block.
+//   moe_grouped<0> act[p, f] = silu(Wg_e[f] . h[token(p)]) * (Wu_e[f] . h[token(p)])   rows gathered through perm
+//   moe_grouped<1> y[perm[p], c] = Wd_e[c] . act[p]                                   rows scattered back
+// A block computes 64 sorted rows of one expert x 64 output columns: 4 warps of 16 rows, mma.sync.m16n8k16 (bf16 in,
+// fp32 accumulate), operands through a two-stage cp.async ring of 64-wide k slices, rows and slices that do not exist
+// filled with zeros on their way in.  Inner sizes are multiples of 16.
+//
+// The grid is sized for the largest number of row tiles there can be (ceil(A/64) + E); blocks beyond the actual number
+// return at once.  No block waits on another block.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 64, BN = 64, BK = 64;
+constexpr int THREADS = 128;
+constexpr int LDS = BK + 8;   // padded row stride (elements)
+constexpr int NT = BN / 8;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+constexpr int SORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(
+    const int* __restrict__ idx, int n_assign, int E, int* __restrict__ offsets, int* __restrict__ perm,
+    int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ n_tiles) {
+  extern __shared__ int sh[];   // counts[E], cursor[E]
+  int* counts = sh;
+  int* cursor = sh + E;
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) counts[e] = 0;
+  __syncthreads();
+  for (int a = threadIdx.x; a < n_assign; a += SORT_THREADS) atomicAdd(&counts[min(max(idx[a], 0), E - 1)], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = run;
+      cursor[e] = run;
+      for (int r = 0; r < counts[e]; r += BM) {
+        tile_expert[tiles] = e;
+        tile_row0[tiles] = run + r;
+        ++tiles;
+      }
+      run += counts[e];
+    }
+    offsets[E] = run;
+    *n_tiles = tiles;
+  }
+  __syncthreads();
+  for (int a = threadIdx.x; a < n_assign; a += SORT_THREADS) perm[atomicAdd(&cursor[min(max(idx[a], 0), E - 1)], 1)] = a;
+}
+
+// MODE 0: A rows are h[perm[p] / top], B is W_gu[e] ([2F, K]: gate rows then up rows), out is act[p, F]
+// MODE 1: A rows are act[p],           B is W_d[e]  ([C, K]),                        out is y[perm[p], C]
+template <int MODE>
+__global__ void __launch_bounds__(THREADS) moe_grouped_kernel(
+    const bf16* __restrict__ a_in, const bf16* __restrict__ w, const int* __restrict__ offsets, const int* __restrict__ perm,
+    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int top, int K,
+    int n_out, bf16* __restrict__ out) {
+  constexpr int NB = MODE == 0 ? 2 * BN : BN;   // weight rows a block reads per k slice
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // [2][BM][LDS]
+  bf16* bs = as + 2 * BM * LDS;                   // [2][NB][LDS]
+  __shared__ int row_src[BM];
+
+  const int tile = blockIdx.x;
+  if (tile >= *n_tiles) return;
+  const int e = tile_expert[tile], p0 = tile_row0[tile];
+  const int rows = min(BM, offsets[e + 1] - p0);
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  if (tid < BM) row_src[tid] = tid < rows ? (MODE == 0 ? perm[p0 + tid] / top : p0 + tid) : -1;
+  __syncthreads();
+  const bf16* we = w + (size_t)e * (MODE == 0 ? 2 * n_out : n_out) * K;
+
+  auto load = [&](int stage, int k0) {
+    bf16* a_st = as + stage * BM * LDS;
+    bf16* b_st = bs + stage * NB * LDS;
+    constexpr int CPR = BK / 8;
+    for (int i = tid; i < BM * CPR; i += THREADS) {
+      const int r = i / CPR, c = i % CPR;
+      const int src = row_src[r];
+      const bool ok = src >= 0 && k0 + c * 8 < K;
+      cp_async16(a_st + r * LDS + c * 8, a_in + (ok ? (size_t)src * K + k0 + c * 8 : 0), ok ? 16 : 0);
+    }
+    for (int i = tid; i < NB * CPR; i += THREADS) {
+      const int r = i / CPR, c = i % CPR;
+      int wr = n0 + (r % BN);
+      const bool ok = wr < n_out && k0 + c * 8 < K;
+      if (MODE == 0 && r >= BN) wr += n_out;   // the matching up rows
+      cp_async16(b_st + r * LDS + c * 8, we + (ok ? (size_t)wr * K + k0 + c * 8 : 0), ok ? 16 : 0);
+    }
+  };
+
+  float acc[MODE == 0 ? 2 : 1][NT][4];
+#pragma unroll
+  for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+
+  const int nk = (K + BK - 1) / BK;
+  load(0, 0);
+  cp_async_commit();
+  for (int ks = 0; ks < nk; ++ks) {
+    const int stage = ks & 1;
+    if (ks + 1 < nk) {
+      load(stage ^ 1, (ks + 1) * BK);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* a_st = as + stage * BM * LDS;
+    const bf16* b_st = bs + stage * NB * LDS;
+#pragma unroll
+    for (int kk = 0; kk < BK / 16; ++kk) {
+      unsigned a0, a1, a2, a3;
+      ldsm_x4(a0, a1, a2, a3, a_st + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m) {
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+          unsigned b0, b1, b2, b3;
+          ldsm_x4(b0, b1, b2, b3, b_st + (m * BN + j * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma16816(acc[m][j], a0, a1, a2, a3, b0, b1);
+          mma16816(acc[m][j + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  const int r0 = warp * 16 + g, r1 = r0 + 8;
+  size_t o0 = 0, o1 = 0;
+  if (MODE == 0) {
+    o0 = (size_t)(p0 + r0) * n_out;
+    o1 = (size_t)(p0 + r1) * n_out;
+  } else {
+    if (r0 < rows) o0 = (size_t)perm[p0 + r0] * n_out;
+    if (r1 < rows) o1 = (size_t)perm[p0 + r1] * n_out;
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int c = n0 + j * 8 + 2 * t;
+    if (c >= n_out) continue;     // n_out is even (a multiple of 16): c + 1 is inside too
+    float v0 = acc[0][j][0], v1 = acc[0][j][1], v2 = acc[0][j][2], v3 = acc[0][j][3];
+    if (MODE == 0) {
+      v0 = v0 / (1.f + expf(-v0)) * acc[MODE == 0 ? 1 : 0][j][0];
+      v1 = v1 / (1.f + expf(-v1)) * acc[MODE == 0 ? 1 : 0][j][1];
+      v2 = v2 / (1.f + expf(-v2)) * acc[MODE == 0 ? 1 : 0][j][2];
+      v3 = v3 / (1.f + expf(-v3)) * acc[MODE == 0 ? 1 : 0][j][3];
+    }
+    if (r0 < rows) *reinterpret_cast<unsigned*>(out + o0 + c) = pack_bf16(v0, v1);
+    if (r1 < rows) *reinterpret_cast<unsigned*>(out + o1 + c) = pack_bf16(v2, v3);
+  }
+}
+
+template <int MODE> constexpr size_t gemm_smem() { return sizeof(bf16) * (size_t)LDS * 2 * (BM + (MODE == 0 ? 2 * BN : BN)); }
+
+template <int MODE>
+int gemm_launch(const void* a_in, const void* w, const int* offsets, const int* perm, const int* tile_expert, const int* tile_row0,
+                const int* n_tiles, int top, int K, int n_out, void* out, int max_tiles, cudaStream_t st) {
+  static bool attr_set = false;   // set by the first (eager) launch, outside any stream capture
+  const size_t smem = gemm_smem<MODE>();
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int n_tiles_n = (n_out + BN - 1) / BN;
+  if (n_tiles_n > 65535) return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid(max_tiles, n_tiles_n);
+  moe_grouped_kernel<MODE><<<grid, THREADS, smem, st>>>((const bf16*)a_in, (const bf16*)w, offsets, perm, tile_expert, tile_row0,
+                                                       n_tiles, top, K, n_out, (bf16*)out);
+  return launch_status();
+}
+}  // namespace
+
+DRYFT_API int dryft_moe_grouped_max_tiles(int n_assign, int E) { return (n_assign + BM - 1) / BM + E; }
+
+// ints the caller provides in `work`: offsets[E+1] | perm[n_assign] | tile_expert[max_tiles] | tile_row0[max_tiles] | n_tiles[1]
+DRYFT_API long long dryft_moe_grouped_work_ints(int n_assign, int E) {
+  return (long long)(E + 1) + n_assign + 2LL * dryft_moe_grouped_max_tiles(n_assign, E) + 1;
+}
+
+// y[n*top, C] = experts of idx[n, top] applied to h[n, W]; act [n*top, F] is scratch (sorted order)
+DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int* idx, int n_tokens, int top,
+                                int E, int W, int F, void* act, void* y, int* work, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (top < 1 || E < 1 || W % 16 || F % 16 || W < 16 || F < 16) return DRYFT_ERR_UNSUPPORTED;
+  const long long n_assign_ll = (long long)n_tokens * top;
+  if (n_assign_ll > (1LL << 30) || (size_t)E * 2 * sizeof(int) > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  const int n_assign = (int)n_assign_ll;
+  const int max_tiles = dryft_moe_grouped_max_tiles(n_assign, E);
+  int* offsets = work;
+  int* perm = offsets + E + 1;
+  int* tile_expert = perm + n_assign;
+  int* tile_row0 = tile_expert + max_tiles;
+  int* n_tiles = tile_row0 + max_tiles;
+  moe_sort_kernel<<<1, SORT_THREADS, sizeof(int) * 2 * E, st>>>(idx, n_assign, E, offsets, perm, tile_expert, tile_row0, n_tiles);
+  int rc = launch_status();
+  if (rc) return rc;
+  rc = gemm_launch<0>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+  if (rc) return rc;
+  return gemm_launch<1>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
+}

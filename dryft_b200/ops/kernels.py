@@ -782,11 +782,102 @@ def moe_combine(y, wts, out) -> None:
 
 
 def diff_attention_prefill_supported(qk_dim: int, v_dim: int, group: int, page: int) -> bool:
-    return False
+    """Whether the tensor-core differential prompt attention exists for these sizes (k16 steps over a map, n8 pairs over
+    the values, 64-token pages)."""
+    return (qk_dim > 0 and qk_dim % 16 == 0 and qk_dim <= 128 and v_dim > 0 and v_dim % 16 == 0 and v_dim <= 256
+            and page == 64 and group >= 1 and 2 * ((64 + 128) * (2 * qk_dim + 8) + 128 * (v_dim + 8)) <= 227 * 1024)
+
+
+def diff_attention_prefill_lib(qk_dim: int, v_dim: int, group: int, page: int) -> ctypes.CDLL:
+    if not diff_attention_prefill_supported(qk_dim, v_dim, group, page):
+        raise KernelError(f"differential prompt attention takes map and value sizes in steps of 16 and 64-token pages, got "
+                          f"{qk_dim}, {v_dim}, {page}")
+    key = ("diff_prefill", qk_dim, v_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("diff_attn_prefill", ("diff_attn_prefill.cu",),
+                                       {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_diff_attn_prefill.argtypes = [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _i, _i, _f, _f, _f, _p]
+            lib.dryft_diff_attn_prefill.restype = _i
+            if (lib.dryft_diff_attn_prefill_qk_dim(), lib.dryft_diff_attn_prefill_v_dim()) != (qk_dim, v_dim):
+                raise KernelError(f"{path} was compiled for other sizes")
+            _variants[key] = lib
+        return lib
+
+
+def diff_attn_prefill(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int, scale: float,
+                      lam: float, sub_eps: float, out_scale: float, window: Optional[int] = None, chunk: Optional[int] = None,
+                      gate=None, gate_col: int = 0) -> None:
+    """``diff_attn_rows``'s result for packed prompts (bfloat16, tensor cores).  Tile ``t`` covers the ``tile_rows[t]`` query
+    tokens from packed index ``tile_tok0[t]`` on, all of one sequence."""
+    n, n_heads, kw = q.shape
+    _need(q, "q", torch.bfloat16)
+    n_kv, page, v_dim = k_pages.shape[1], k_pages.shape[2], v_pages.shape[3]
+    _need(k_pages, "k_pages", torch.bfloat16, (None, n_kv, page, kw))
+    _need(v_pages, "v_pages", torch.bfloat16, (k_pages.shape[0], n_kv, page, v_dim))
+    for t, nm in ((page_table, "page_table"), (tile_tok0, "tile_tok0"), (tile_rows, "tile_rows"), (tok_slot, "tok_slot"),
+                  (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if tile_tok0.numel() < n_tiles or tile_rows.numel() < n_tiles:
+        raise KernelError("diff_attn_prefill: tile arrays shorter than the tile count")
+    _need(out, "attention output", torch.bfloat16, (n, n_heads * v_dim))
+    if n_heads % n_kv or kw % 2:
+        raise KernelError(f"diff_attn_prefill: {n_heads} query heads / {n_kv} kv heads / key rows of {kw}")
+    gate_ptr, gate_stride = None, 0
+    if gate is not None:
+        _need(gate, "gate", torch.bfloat16)
+        if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+            raise KernelError("diff_attn_prefill: gate columns outside the gate tensor")
+        gate_ptr, gate_stride = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    lib = diff_attention_prefill_lib(kw // 2, v_dim, n_heads // n_kv, page)
+    _ok(lib.dryft_diff_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(tile_tok0),
+                                    _ptr(tile_rows), _ptr(tok_slot), _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), n_tiles,
+                                    n_heads, n_kv, float(scale), int(window or 0), int(chunk or 0), float(lam), float(sub_eps),
+                                    float(out_scale), _stream()), f"diff_attn_prefill (dims {kw // 2}, {v_dim})")
+
+
+_moe_grouped: Optional[ctypes.CDLL] = None
 
 
 def moe_grouped_supported(hidden: int, inter: int) -> bool:
-    return False
+    """Whether the grouped tensor-core expert products take these inner sizes (k16 steps, 16-byte rows)."""
+    return hidden >= 16 and inter >= 16 and hidden % 16 == 0 and inter % 16 == 0
+
+
+def moe_grouped_lib() -> ctypes.CDLL:
+    global _moe_grouped
+    with _lock:
+        if _moe_grouped is None:
+            lib = _load(build.build_library("moe_grouped", ("moe_grouped.cu",)))
+            lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p]
+            lib.dryft_moe_grouped.restype = _i
+            lib.dryft_moe_grouped_work_ints.argtypes = [_i, _i]
+            lib.dryft_moe_grouped_work_ints.restype = _ll
+            _moe_grouped = lib
+        return _moe_grouped
+
+
+def moe_grouped(h, w_gate_up, w_down, idx, y) -> None:
+    """``y[n*top + k] = expert idx[n, k] applied to h[n]`` (bfloat16) with the assignments sorted by expert on the device and
+    both expert products as grouped tensor-core products (``csrc/moe_grouped.cu``: three launches, no host round trip)."""
+    n, width = h.shape
+    top = idx.shape[1]
+    e, two_f, _ = w_gate_up.shape
+    f = two_f // 2
+    _need(h, "h", torch.bfloat16)
+    _need(idx, "idx", torch.int32, (n, top))
+    _need(w_gate_up, "w_gate_up", torch.bfloat16, (e, 2 * f, width))
+    _need(w_down, "w_down", torch.bfloat16, (e, width, f))
+    _need(y, "y", torch.bfloat16, (n * top, width))
+    if not moe_grouped_supported(width, f):
+        raise KernelError(f"moe_grouped: inner sizes must be multiples of 16, got {width}, {f}")
+    lib = moe_grouped_lib()
+    work = torch.empty(int(lib.dryft_moe_grouped_work_ints(n * top, e)), dtype=torch.int32, device=h.device)
+    act = torch.empty((n * top, f), dtype=torch.bfloat16, device=h.device)
+    _ok(lib.dryft_moe_grouped(_ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(idx), n, top, e, width, f, _ptr(act), _ptr(y), _ptr(work),
+                              _stream()), f"moe_grouped ({e} experts, {width} x {f})", n_kernels=3)
 
 
 # ----------------------------------------------------------------------------- matrix products

@@ -37,11 +37,13 @@ from ..config.spec import PartSpec
 
 class TensorInfo(NamedTuple):
     """One checkpoint tensor a part expects.  ``kind``: "matrix" (a product's weight), "vector"
-    (norm weights and other 1-D tensors, kept in 32-bit on the device) or "table" (embedding)."""
+    (norm weights and other 1-D tensors, kept in 32-bit on the device) or "table" (embedding).  ``mean``: what random
+    weights of this tensor are drawn around (default: 1 for vectors, 0 for everything else)."""
 
     shape: Tuple[int, ...]
     kind: str
     optional: bool = False
+    mean: Optional[float] = None
 
 
 @dataclass

@@ -59,7 +59,7 @@ class DiffAttention:
             nm["q_norm"]: TensorInfo((d,), "vector"),
         }
         for role in ("lq1", "lk1", "lq2", "lk2"):
-            t[nm[role]] = TensorInfo((d,), "vector")
+            t[nm[role]] = TensorInfo((d,), "vector", False, 0.0)   # drawn around zero: lambda stays near `diff`
         if params.get("gate", True):
             t[nm["gate"]] = TensorInfo((nh, w), "matrix")
         if params.get("own_kv", True):

@@ -56,7 +56,8 @@ class OffsetRMSNorm:
 
     @staticmethod
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
-        return {prefix + params.get("name", "weight"): TensorInfo((params["size"],), "vector")}
+        # random weights are drawn around 1 - offset, so that the factor (offset + w) is around 1
+        return {prefix + params.get("name", "weight"): TensorInfo((params["size"],), "vector", False, 1.0 - float(params.get("offset", 1.0)))}
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
         self.size = int(params["size"])

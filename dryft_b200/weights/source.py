@@ -91,14 +91,15 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 def random_tensor(name: str, info: TensorInfo, seed: int, std: float, device: torch.device) -> torch.Tensor:
     """float32 values of one tensor: matrices and tables ``normal(0, std)``, vectors (norm weights)
-    ``1 + normal(0, std)``.  Each tensor has its own generator seeded from (seed, name), so the
+    ``1 + normal(0, std)``, or around ``info.mean`` where the part names one.  Each tensor has its own generator seeded from (seed, name), so the
     values do not depend on the order tensors are asked for.  (The reference only has random
     weights through its tooling, ``agent/verify.py:36-54``.)"""
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
     t = torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device) * std
-    if info.kind == "vector":
-        t += 1.0
+    mean = info.mean if info.mean is not None else (1.0 if info.kind == "vector" else 0.0)
+    if mean:
+        t += mean
     return t
 
 

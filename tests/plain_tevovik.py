@@ -41,15 +41,6 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, pos: torch.Te
     return table[tokens] * scale + sinusoid_positions(pos, table.shape[1], table.dtype)
 
 
-def chunk_mask(pos: torch.Tensor, chunk: Optional[int]) -> torch.Tensor:
-    """``[T, T]`` bool: query i sees key j iff ``j <= i`` and both lie in the same block of ``chunk`` positions."""
-    i, j = pos[:, None], pos[None, :]
-    m = j <= i
-    if chunk:
-        m = m & (torch.div(i, chunk, rounding_mode="floor") == torch.div(j, chunk, rounding_mode="floor"))
-    return m
-
-
 def diff_lambda(lq1, lk1, lq2, lk2, diff: float) -> float:
     return math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + diff
 
@@ -64,19 +55,21 @@ def project_keys_values(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str
     return k, v
 
 
-def diff_attention(h: torch.Tensor, pos: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, m: Mapping, eps: float,
-                   k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    """The mixer's output ``[T, W]`` given the keys and values it reads (its own or another layer's)."""
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    diff, scale = float(m["diff"]), float(m["scale"])
-    chunk = (m.get("mask") or {}).get("size")
-    T = h.shape[0]
-    q = (h @ t[pre + "q"].T).reshape(T, H, 2, d)
-    q = rms_unit(q, eps) * t[pre + "q.norm"]
-    lam = diff_lambda(t[pre + "lq1"], t[pre + "lk1"], t[pre + "lq2"], t[pre + "lk2"], diff)
-    gate = torch.sigmoid(h @ t[pre + "g"].T)            # [T, H]
-    mask = chunk_mask(pos, chunk)
-    heads: List[torch.Tensor] = []
+def diff_attention_core(q, k, v, gate, pos, *, scale: float, lam: float, diff: float, eps: float,
+                        chunk: Optional[int] = None, window: Optional[int] = None, key_pos: Optional[torch.Tensor] = None):
+    """Heads' outputs ``[T, H, dv]`` from normalised queries ``q [T, H, 2, d]``, keys ``k [S, G, 2, d]``, values
+    ``v [S, G, dv]`` and gate logits ``gate [T, H]`` (or None).  ``key_pos`` are the keys' positions (default: the
+    queries' own, ``S = T``)."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    kp = pos if key_pos is None else key_pos
+    i, j = pos[:, None], kp[None, :]
+    mask = j <= i
+    if chunk:
+        mask = mask & (torch.div(i, chunk, rounding_mode="floor") == torch.div(j, chunk, rounding_mode="floor"))
+    if window:
+        mask = mask & (i - j < window)
+    out = []
     for hd in range(H):
         g = hd // (H // G)
         maps = []
@@ -86,8 +79,24 @@ def diff_attention(h: torch.Tensor, pos: torch.Tensor, t: Mapping[str, torch.Ten
             maps.append(torch.softmax(s, dim=-1) @ v[:, g])
         o = maps[0] - lam * maps[1]
         o = rms_unit(o, eps) * (1.0 - diff)
-        heads.append(o * gate[:, hd:hd + 1])
-    return torch.cat(heads, dim=-1) @ t[pre + "o"].T
+        if gate is not None:
+            o = o * torch.sigmoid(gate[:, hd:hd + 1])
+        out.append(o)
+    return torch.stack(out, dim=1)
+
+
+def diff_attention(h: torch.Tensor, pos: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, m: Mapping, eps: float,
+                   k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """The mixer's output ``[T, W]`` given the keys and values it reads (its own or another layer's)."""
+    H, d = m["heads"], m["dim"]
+    diff = float(m["diff"])
+    T = h.shape[0]
+    q = (h @ t[pre + "q"].T).reshape(T, H, 2, d)
+    q = rms_unit(q, eps) * t[pre + "q.norm"]
+    lam = diff_lambda(t[pre + "lq1"], t[pre + "lk1"], t[pre + "lq2"], t[pre + "lk2"], diff)
+    o = diff_attention_core(q, k, v, h @ t[pre + "g"].T, pos, scale=float(m["scale"]), lam=lam, diff=diff, eps=eps,
+                            chunk=(m.get("mask") or {}).get("size"))
+    return o.reshape(T, -1) @ t[pre + "o"].T
 
 
 def route(h: torch.Tensor, w_router: torch.Tensor, r: Mapping):
@@ -146,3 +155,14 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens, dtype=
         if layers_out is not None:
             layers_out.append(x.clone())
     return norm_one_plus(x, t["final.norm"], eps) @ t["head"].T
+
+
+def greedy(config: Mapping, tensors: Mapping[str, torch.Tensor], prompt, n_new: int, dtype=torch.float64) -> List[int]:
+    """``n_new`` tokens chosen greedily (first index on ties), the whole sequence evaluated anew each time."""
+    toks = list(prompt)
+    out = []
+    for _ in range(n_new):
+        nxt = int(forward(config, tensors, toks, dtype)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out

@@ -1,0 +1,212 @@
+"""The Tevovik decoder in the engine against the plain evaluation (``plain_tevovik.py``), in 32-bit (sharp) and in
+bfloat16: whole prompts, prompts against token-by-token decoding, prompts in portions down to two tokens, unequal
+batches against each request alone, slots and pages used again (with poisoned pages), long decoding across chunk and
+page edges, the first tokens, and greedy generation through ``Engine.generate`` / ``generate_many``."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_tevovik as P
+import tevovik_models as M
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+_cache = {}
+
+
+def model(name, tmp_path_factory):
+    if name not in _cache:
+        cfg = M.CONFIGS[name]
+        tensors = M.draw_weights(cfg, seed=11 + len(name) + ord(name[0]))
+        d = M.write_model(cfg, tensors, str(tmp_path_factory.mktemp(f"tevovik_{name}")))
+        _cache[name] = (cfg, tensors, d, {})
+    return _cache[name]
+
+
+def plain_logits(entry, tokens):
+    cfg, tensors, _, memo = entry
+    key = tuple(tokens)
+    if key not in memo:
+        memo[key] = P.forward(cfg, tensors, tokens, torch.float64)
+    return memo[key]
+
+
+def engine(entry, dtype, **kw):
+    from dryft_b200.engine.api import Engine, EngineOptions
+
+    opts = dict(dtype=dtype, max_batch=8, max_seq_len=512, max_tokens=2048, cuda_graphs=False)
+    opts.update(kw)
+    return Engine(entry[2], EngineOptions(**opts))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_whole_prompts_decoding_portions_and_batches(tmp_path_factory, name, dtype):
+    entry = model(name, tmp_path_factory)
+    cfg = entry[0]
+    eng = engine(entry, dtype)
+    lengths = [1, 2, 23, 65, 131, 200]
+    reqs = M.prompts(cfg, lengths, seed=3)
+    with torch.inference_mode():
+        # whole prompts, logits at every place (the first tokens included)
+        for toks in reqs:
+            s = eng.cache.open_sequences(1)
+            got = eng.stepper.step(s, [toks], [list(range(len(toks)))])
+            eng.cache.close_sequences(s)
+            M.assert_close(got, plain_logits(entry, toks), dtype, f"{name} whole prompt of {len(toks)}")
+        # most of the prompt at once, the rest token by token (across chunk and page edges)
+        for toks in reqs[3:]:
+            head = max(1, len(toks) - 70)
+            s = eng.cache.open_sequences(1)
+            rows = [eng.stepper.step(s, [toks[:head]], [[head - 1]])]
+            for t in range(head, len(toks)):
+                rows.append(eng.stepper.step(s, [[toks[t]]], [[0]]))
+            eng.cache.close_sequences(s)
+            M.assert_close(torch.cat(rows), plain_logits(entry, toks)[head - 1:], dtype, f"{name} decoding {len(toks)}")
+        # portions of several sizes, down to two tokens
+        for portion in (2, 7, 64, 97):
+            toks = reqs[4]
+            s = eng.cache.open_sequences(1)
+            rows = []
+            for c0 in range(0, len(toks), portion):
+                piece = toks[c0:c0 + portion]
+                rows.append(eng.stepper.step(s, [piece], [list(range(len(piece)))]))
+            eng.cache.close_sequences(s)
+            M.assert_close(torch.cat(rows), plain_logits(entry, toks), dtype, f"{name} portions of {portion}")
+        # an unequal batch of prompts, then decoded together; shorter requests end earlier
+        batch = [reqs[2], reqs[5], reqs[3], reqs[1]]
+        heads = [max(1, len(t) - 12) for t in batch]
+        slots = eng.cache.open_sequences(len(batch))
+        got = eng.stepper.step(slots, [t[:h] for t, h in zip(batch, heads)], [list(range(h)) for h in heads])
+        at = 0
+        for t, h in zip(batch, heads):
+            M.assert_close(got[at:at + h], plain_logits(entry, t)[:h], dtype, f"{name} batched prompt of {h}")
+            at += h
+        live = list(range(len(batch)))
+        step = 0
+        collected = {b: [] for b in live}
+        while live:
+            got = eng.stepper.step([slots[b] for b in live], [[batch[b][heads[b] + step]] for b in live], [[0]] * len(live))
+            for r, b in enumerate(live):
+                collected[b].append(got[r:r + 1])
+            step += 1
+            done = [b for b in live if heads[b] + step >= len(batch[b])]
+            eng.cache.close_sequences([slots[b] for b in done])
+            live = [b for b in live if b not in done]
+        for b, rows in collected.items():
+            M.assert_close(torch.cat(rows), plain_logits(entry, batch[b])[heads[b]:], dtype, f"{name} batched decoding of request {b}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pages_and_slots_used_again_hold_nothing_of_their_last_holder(tmp_path_factory, dtype):
+    entry = model("a", tmp_path_factory)
+    cfg = entry[0]
+    # room for little more than one request: every request reuses the pages of the one before
+    eng = engine(entry, dtype, max_batch=2, max_seq_len=256, max_tokens=256)
+    reqs = M.prompts(cfg, [150, 90, 201, 33], seed=5)
+    with torch.inference_mode():
+        for i, toks in enumerate(reqs):
+            s = eng.cache.open_sequences(1)
+            head = len(toks) - 9
+            rows = [eng.stepper.step(s, [toks[:head]], [list(range(head))])]
+            for t in range(head, len(toks)):
+                rows.append(eng.stepper.step(s, [[toks[t]]], [[0]]))
+            eng.cache.close_sequences(s)
+            M.assert_close(torch.cat(rows), plain_logits(entry, toks), dtype, f"request {i} on reused pages")
+            # what the freed pages hold must never matter again
+            for g in eng.cache._groups:
+                g.k.fill_(float("nan"))
+                g.v.fill_(float("nan"))
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_gives_pages_of_finished_chunks_back(tmp_path_factory, dtype):
+    entry = model("a", tmp_path_factory)
+    cfg = entry[0]
+    eng = engine(entry, dtype, max_batch=2, max_seq_len=512, max_tokens=1024)
+    toks = M.prompts(cfg, [300], seed=9)[0]
+    with torch.inference_mode():
+        s = eng.cache.open_sequences(1)
+        rows = [eng.stepper.step(s, [toks[:3]], [[0, 1, 2]])]
+        for t in range(3, len(toks)):
+            rows.append(eng.stepper.step(s, [[toks[t]]], [[0]]))
+        # layers 0 and 1 share one cache entry and the chunk of 20; layer 2 has a chunk of 64: both groups trim
+        held = [len(g.ledger.held(s[0])) for g in eng.cache._groups]
+        assert all(h <= 2 for h in held), held
+        eng.cache.close_sequences(s)
+    M.assert_close(torch.cat(rows), plain_logits(entry, toks), dtype, "300 tokens, nearly all decoded one by one")
+
+
+def test_a_borrower_with_another_chunk_keeps_the_owners_pages(tmp_path_factory):
+    entry = model("b", tmp_path_factory)    # layer 1 reads layer 0's keys with a smaller chunk than layer 0's
+    eng = engine(entry, "float32")
+    toks = M.prompts(entry[0], [260], seed=1)[0]
+    with torch.inference_mode():
+        s = eng.cache.open_sequences(1)
+        got = eng.stepper.step(s, [toks], [list(range(len(toks)))])
+        assert len(eng.cache._groups) == 1 and len(eng.cache._groups[0].ledger.held(s[0])) == 5   # nothing given back
+        eng.cache.close_sequences(s)
+    M.assert_close(got, plain_logits(entry, toks), "float32", "borrowed keys under another chunk size")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(tmp_path_factory, dtype):
+    entry = model("c", tmp_path_factory)
+    cfg, tensors = entry[0], entry[1]
+    eng = engine(entry, dtype, cuda_graphs=True, max_batch=4)
+    prompts = M.prompts(cfg, [5, 19, 40], seed=21)
+    n_new = 12
+    steps = list(eng.generate(prompts, n_new))
+    got = [[st[b] for st in steps] for b in range(len(prompts))]
+    many = eng.generate_many(prompts + prompts[:2], n_new)
+    assert many[:3] == got and many[3:] == got[:2]
+    if dtype == "float32":
+        for b, p in enumerate(prompts):
+            assert got[b] == P.greedy(cfg, tensors, p, n_new), f"request {b}"
+    else:
+        # bfloat16 may legitimately part ways at a close call; until then the tokens are the plain ones
+        agree = 0
+        for b, p in enumerate(prompts):
+            want = P.greedy(cfg, tensors, p, n_new)
+            agree += sum(1 for x, y in zip(got[b], want) if x == y)
+        assert agree >= 0.6 * n_new * len(prompts)
+    # graphs and eager steps choose the same tokens
+    eager = engine(entry, dtype, cuda_graphs=False, max_batch=4)
+    assert eager.generate_many(prompts, n_new) == got
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_as_a_child_process(tmp_path_factory, tmp_path, dtype):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import helpers as H
+
+    entry = model("a", tmp_path_factory)
+    cfg = entry[0]
+    reqs = M.prompts(cfg, [70, 31, 2], seed=33)
+    out = str(tmp_path / "out")
+    steps = [{"step": 0, "entries": [{"id": f"r{i}", "tokens": t[:-1] if len(t) > 2 else t[:1], "want": [0, len(t) - 2] if len(t) > 2 else [0]}
+                                     for i, t in enumerate(reqs)], "end": []},
+             {"step": 1, "entries": [{"id": f"r{i}", "tokens": [t[-1]], "want": [0]} for i, t in enumerate(reqs)], "end": ["r0", "r1", "r2"]},
+             {"step": 2, "entries": [{"id": "r0", "tokens": reqs[1], "want": []}], "end": []},
+             {"step": 3, "entries": [{"id": "r0", "tokens": [5], "want": [0]}], "end": ["r0"]}]
+    proc = subprocess.run([sys.executable, os.path.join(H.ROOT, "bin", "trace_run"), "--model", entry[2], "--dtype", dtype,
+                           "--out", out, "--max-tokens", "256"], input="".join(json.dumps(s) + "\n" for s in steps),
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not os.path.exists(os.path.join(out, "2.f32"))
+    got0 = torch.from_numpy(np.fromfile(os.path.join(out, "0.f32"), dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+    want0 = torch.cat([plain_logits(entry, t)[[0, len(t) - 2] if len(t) > 2 else [0]] for t in reqs])
+    M.assert_close(got0, want0, dtype, "replayed prompts")
+    got1 = torch.from_numpy(np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+    M.assert_close(got1, torch.cat([plain_logits(entry, t)[-1:] for t in reqs]), dtype, "replayed decode step")
+    got3 = torch.from_numpy(np.fromfile(os.path.join(out, "3.f32"), dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+    M.assert_close(got3, plain_logits(entry, reqs[1] + [5])[-1:], dtype, "a request id used again")
