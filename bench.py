@@ -109,7 +109,7 @@ def decode_device_time(eng, batch, prompt_len, steps, warmup, seed):
     from dryft_b200.ops import kernels as K
     from dryft_b200.sampling.sampler import SamplingParams, choose
 
-    prompts = random_prompts(batch, prompt_len, eng.config.vocab_size, seed)
+    prompts = random_prompts(batch, prompt_len, eng.spec.vocab_size, seed)
     params = SamplingParams()
     with torch.inference_mode():
         slots = eng.cache.open_sequences(batch)
@@ -152,7 +152,7 @@ def decode_e2e(eng, batch, prompt_len, steps, seed):
     """The same through Engine.generate: host lists in, a host list out per step."""
     import torch
 
-    prompts = random_prompts(batch, prompt_len, eng.config.vocab_size, seed)
+    prompts = random_prompts(batch, prompt_len, eng.spec.vocab_size, seed)
     be = eng._backend
     for _ in eng.generate(prompts, 4):  # warm-up of this batch shape
         pass
@@ -175,7 +175,7 @@ def decode_e2e(eng, batch, prompt_len, steps, seed):
 def prefill_time(eng, tokens, iters, seed):
     import torch
 
-    prompt = random_prompts(1, tokens, eng.config.vocab_size, seed)[0]
+    prompt = random_prompts(1, tokens, eng.spec.vocab_size, seed)[0]
     times = []
     with torch.inference_mode():
         for i in range(iters + 2):
@@ -190,6 +190,45 @@ def prefill_time(eng, tokens, iters, seed):
             if i >= 2:
                 times.append(s.elapsed_time(e))
     return statistics.median(times)
+
+
+# ----------------------------------------------------------------------------- two designs at equal size
+def compare_arm(args, warmup) -> int:
+    """Prefill and decode throughput of Tevovik shapes, each beside the dense shape of equal size (same width, layers,
+    heads, vocabulary; the dense intermediate size is the expert size times the experts a token uses).  One JSON line."""
+    import torch
+
+    from dryft_b200.config import config_from_dict, preset
+    from dryft_b200.config.presets import EQUAL_SIZE
+    from dryft_b200.engine.api import Engine
+
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    steps = min(args.steps, 128)
+    rows = {}
+    for name in args.compare.split(","):
+        if name not in EQUAL_SIZE:
+            print(f"bench.py: --compare knows {sorted(EQUAL_SIZE)}, not {name!r}")
+            return 2
+        for shape in (name, EQUAL_SIZE[name]):
+            cfg = config_from_dict(preset(shape))
+            ctx_cap = max(args.prompt_len + steps + warmup + 64, 2048 + 64)
+            eng = Engine.from_config(cfg, seed=args.seed, dtype="bfloat16", max_batch=8, max_seq_len=ctx_cap, max_tokens=8 * (ctx_cap + 64))
+            torch.cuda.synchronize()
+            T = 2048
+            pf_ms = prefill_time(eng, T, 5, args.seed + 2)
+            r = {"prefill_tok_s": T / (pf_ms * 1e-3), "prefill_ms": pf_ms,
+                 "prefill_matmul_tflops": (cfg.matmul_flops_per_token() * T + 2 * eng.spec.vocab_size * eng.spec.hidden_size) / (pf_ms * 1e-3) / 1e12}
+            for b in (1, 8):
+                ms, launches, mean_ctx = decode_device_time(eng, b, args.prompt_len, steps, warmup, args.seed + b)
+                wb = cfg.weight_bytes_per_decode_step(2, b) if shape in EQUAL_SIZE else cfg.weight_bytes_per_decode_step(2)
+                r[f"decode_b{b}"] = {"tok_s": b * 1000.0 / ms, "ms_per_step": ms, "launches_per_step": launches / steps,
+                                     "weight_gb_s": wb / (ms * 1e-3) / 1e9, "frac_of_copy_bandwidth": wb / (ms * 1e-3) / 1e9 / hbm_gbs}
+            rows[shape] = r
+            del eng
+            torch.cuda.empty_cache()
+    print(json.dumps({"compare": rows, "dtype": "bf16", "steps": steps, "warmup": warmup, "prompt_len": args.prompt_len,
+                      "data": "synthetic: seeded uniform token ids, random normal(0,0.02) weights", "peaks": peak_src}))
+    return 0
 
 
 # ----------------------------------------------------------------------------- the reference arm
@@ -345,6 +384,9 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="time only one phase (for profiling); the JSON line then carries only that phase")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--compare", default=None, metavar="SHAPE[,SHAPE]",
+                    help="instead of the default workload: prefill (2,048 tokens) and decode (batch 1 and 8) of these Tevovik "
+                         "presets, each beside the dense Qwen3 preset of equal size (tevovik-1k, tevovik-2k)")
     ap.add_argument("--small-m-max", type=int, default=None,
                     help="rows up to which decode products stream weights themselves (the engine's default if not given)")
     ap.add_argument("--engine-opt", action="append", default=[], metavar="NAME=VALUE",
@@ -357,6 +399,8 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
     warmup = max(3, args.warmup)
+    if args.compare:
+        return compare_arm(args, warmup)
 
     import torch
 

@@ -53,6 +53,46 @@ PRESETS = {
 }
 
 
+def _tevovik(width: int, layers: int, heads: int, kv_heads: int, dim: int, vdim: int, chunk: int, experts: int, ff: int, top: int,
+             groups: int, keep: int, vocab: int, share_every: int = 3) -> dict:
+    """A Tevovik ``config.json``: every ``share_every``-th layer reads the keys and values of the layer before it."""
+    out = []
+    for i in range(layers):
+        mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "diff": 0.4,
+                 "mask": {"size": chunk}}
+        if share_every and i % share_every == share_every - 1:
+            mixer["kv_from"] = i - 1
+        out.append({"type": "attention", "mixer": mixer,
+                    "mlp": {"kind": "moe", "expert": {"ff": ff},
+                            "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}})
+    return {"architecture": "Tevovik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": out}
+
+
+# Tevovik shapes with layers the size of a real model's, and beside each the dense Qwen3 shape of equal size: the same
+# width, layer count, head counts and vocabulary, a head size equal to the value size, and an intermediate size equal
+# to the expert size times the experts a token uses (equal weights read and equal flops per token).
+PRESETS.update({
+    "tevovik-tiny": _tevovik(width=64, layers=3, heads=4, kv_heads=2, dim=16, vdim=32, chunk=48, experts=8, ff=32, top=2,
+                             groups=4, keep=2, vocab=256),
+    "tevovik-1k": _tevovik(width=1024, layers=8, heads=8, kv_heads=2, dim=64, vdim=128, chunk=1024, experts=32, ff=512, top=4,
+                           groups=4, keep=2, vocab=32768),
+    "qwen3-1k": _qwen3(
+        num_hidden_layers=8, hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+        intermediate_size=2048, vocab_size=32768, rope_theta=1000000.0, rms_norm_eps=1e-6,
+        tie_word_embeddings=False, max_position_embeddings=8192,
+    ),
+    "tevovik-2k": _tevovik(width=2048, layers=12, heads=16, kv_heads=4, dim=64, vdim=128, chunk=2048, experts=64, ff=768, top=8,
+                           groups=8, keep=4, vocab=65536),
+    "qwen3-2k": _qwen3(
+        num_hidden_layers=12, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
+        intermediate_size=6144, vocab_size=65536, rope_theta=1000000.0, rms_norm_eps=1e-6,
+        tie_word_embeddings=False, max_position_embeddings=8192,
+    ),
+})
+EQUAL_SIZE = {"tevovik-1k": "qwen3-1k", "tevovik-2k": "qwen3-2k"}   # a Tevovik shape -> the dense shape of equal size
+
+
 def preset(name: str) -> dict:
     if name not in PRESETS:
         raise KeyError(f"unknown preset {name!r}; known: " + ", ".join(sorted(PRESETS)))

@@ -135,7 +135,7 @@ class TevovikConfig:
             if kv_from is not None:
                 src = mixers[kv_from]
                 if (src.kv_heads, src.dim, src.vdim) != (mix.kv_heads, mix.dim, mix.vdim):
-                    raise ConfigError(f"config.json: {mw} reads layer {kv_from}'s keys and values but differs from it in kv_heads, dim or vdim")
+                    raise ConfigError(f"config.json: {mw}.kv_from names layer {kv_from}, which differs from this layer in kv_heads, dim or vdim")
             mixers.append(mix)
             mlp = layer.get("mlp")
             if mlp is None:

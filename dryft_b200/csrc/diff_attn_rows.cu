@@ -242,8 +242,8 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
     out[((size_t)n * nH + (size_t)kvh * G) * DV + i] = from_f32<T>(ob[i] * ssq[i / DV]);
 }
 
-// Combine the partials of one (row, head): per map  w_s = exp(m_s - max m),  a = sum w_s acc_s / sum w_s l_s ; then the
-// same epilogue as above.
+// Combine the partials of one (row, head): per map  w_s = exp(m_s - max m) / sum_s' w_s' l_s',  a = sum w_s acc_s ; then
+// the same epilogue as above.
 template <typename T>
 __global__ void __launch_bounds__(THREADS) diff_attn_reduce_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ tok_slot,
@@ -251,28 +251,31 @@ __global__ void __launch_bounds__(THREADS) diff_attn_reduce_kernel(
     float out_scale) {
   __shared__ float o_s[DV];
   __shared__ float scratch[33];
+  extern __shared__ float wgt[];   // [MAPS][n_splits]: each split's share exp(m_s - max m) / sum, worked out once
   const size_t rh = blockIdx.x;  // row * nH + head
   const int n = (int)(rh / nH), h = (int)(rh % nH);
-  float mx[MAPS], denom[MAPS];
-#pragma unroll
-  for (int m = 0; m < MAPS; ++m) {
+  if (threadIdx.x < MAPS * 32) {   // one warp per map
+    const int m = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float* ml = part_ml + (rh * MAPS + m) * n_splits * 2;
-    mx[m] = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx[m] = fmaxf(mx[m], ml[s * 2]);
-    denom[m] = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-      if (ml[s * 2] != -INFINITY) denom[m] += expf(ml[s * 2] - mx[m]) * ml[s * 2 + 1];
+    float mx = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, ml[s * 2]);
+    mx = warp_max(mx);
+    float denom = 0.f;
+    for (int s = lane; s < n_splits; s += 32)
+      if (ml[s * 2] != -INFINITY) denom += expf(ml[s * 2] - mx) * ml[s * 2 + 1];
+    denom = warp_sum(denom);
+    for (int s = lane; s < n_splits; s += 32)
+      wgt[m * n_splits + s] = (ml[s * 2] != -INFINITY && denom > 0.f) ? expf(ml[s * 2] - mx) / denom : 0.f;
   }
+  __syncthreads();
   float ss = 0.f;
   for (int d = threadIdx.x; d < DV; d += THREADS) {
     float a[MAPS];
 #pragma unroll
     for (int m = 0; m < MAPS; ++m) {
-      const float* ml = part_ml + (rh * MAPS + m) * n_splits * 2;
       float num = 0.f;
-      for (int s = 0; s < n_splits; ++s)
-        if (ml[s * 2] != -INFINITY) num += expf(ml[s * 2] - mx[m]) * part_o[((rh * MAPS + m) * n_splits + s) * DV + d];
-      a[m] = denom[m] > 0.f ? num / denom[m] : 0.f;
+      for (int s = 0; s < n_splits; ++s) num = fmaf(wgt[m * n_splits + s], part_o[((rh * MAPS + m) * n_splits + s) * DV + d], num);
+      a[m] = num;
     }
     const float o = a[0] - lambda * a[1];
     o_s[d] = o;
@@ -291,7 +294,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
            int n_rows, int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale,
            cudaStream_t st) {
   if (n_rows <= 0) return 0;
-  if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 65535) return DRYFT_ERR_UNSUPPORTED;
+  if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 4096) return DRYFT_ERR_UNSUPPORTED;
   if (n_splits > 1 && (!part_o || !part_ml)) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = Smem<T>::bytes();
   if (smem > 227 * 1024) return DRYFT_ERR_UNSUPPORTED;
@@ -313,7 +316,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
                                                        nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale);
   int rc = launch_status();
   if (rc || n_splits == 1) return rc;
-  diff_attn_reduce_kernel<T><<<(unsigned)((size_t)n_rows * nKV * G), THREADS, 0, st>>>(
+  diff_attn_reduce_kernel<T><<<(unsigned)((size_t)n_rows * nKV * G), THREADS, sizeof(float) * MAPS * n_splits, st>>>(
       part_o, part_ml, tok_slot, (const T*)gate, gate_stride, (T*)out, nKV * G, n_splits, lambda, sub_eps, out_scale);
   return launch_status();
 }

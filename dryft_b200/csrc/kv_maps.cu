@@ -16,6 +16,11 @@
 namespace {
 constexpr int THREADS = 128;
 
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
     const T* __restrict__ proj, int stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
@@ -27,6 +32,8 @@ __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
   const int slot = tok_slot[n];
   const T* row = proj + (size_t)n * stride;
   const int nq = nH * maps, nk = write_kv ? nKV * maps : 0, nv = write_kv ? nKV : 0;
+  // pairs of elements where every vector starts on an even element (row stride, D and DV even)
+  const bool pairs = ((stride | D | DV) & 1) == 0;
   T* krow = nullptr;
   T* vrow = nullptr;
   if (write_kv && slot >= 0) {
@@ -53,6 +60,34 @@ __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
         for (int c = lane; c < D; c += 32) dst[c] = from_f32<T>(0.f);
         continue;
       }
+      const float* w = is_q ? q_w : k_w;
+      if (pairs) {   // two elements a lane and trip; a vector of up to 128 stays in registers between the two passes
+        float2 keep[2];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c = 2 * (lane + 32 * i);
+          keep[i] = make_float2(0.f, 0.f);
+          if (c < D) keep[i] = load2(src + c);
+          ss = fmaf(keep[i].x, keep[i].x, fmaf(keep[i].y, keep[i].y, ss));
+        }
+        for (int c = 128 + 2 * lane; c < D; c += 64) {
+          const float2 x = load2(src + c);
+          ss = fmaf(x.x, x.x, fmaf(x.y, x.y, ss));
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c = 2 * (lane + 32 * i);
+          if (c < D) store2(dst + c, keep[i].x * inv * (w ? w[c] : 1.f), keep[i].y * inv * (w ? w[c + 1] : 1.f));
+        }
+        for (int c = 128 + 2 * lane; c < D; c += 64) {
+          const float2 x = load2(src + c);
+          store2(dst + c, x.x * inv * (w ? w[c] : 1.f), x.y * inv * (w ? w[c + 1] : 1.f));
+        }
+        continue;
+      }
       float ss = 0.f;
       for (int c = lane; c < D; c += 32) {
         const float x = to_f32<T>(src[c]);
@@ -60,7 +95,6 @@ __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
       }
       ss = warp_sum(ss);
       const float inv = 1.f / sqrtf(ss / (float)D + eps);
-      const float* w = is_q ? q_w : k_w;
       for (int c = lane; c < D; c += 32) {
         const float x = to_f32<T>(src[c]) * inv;
         dst[c] = from_f32<T>(w ? x * w[c] : x);
@@ -70,7 +104,14 @@ __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
       const int g = u - nq - nk;
       const T* src = row + (size_t)(nq + nk) * D + (size_t)g * DV;
       T* dst = vrow + (size_t)g * page_size * DV;
-      for (int c = lane; c < DV; c += 32) dst[c] = src[c];
+      if (pairs) {
+        for (int c = 2 * lane; c < DV; c += 64) {
+          const float2 x = load2(src + c);
+          store2(dst + c, x.x, x.y);
+        }
+      } else {
+        for (int c = lane; c < DV; c += 32) dst[c] = src[c];
+      }
     }
   }
 }

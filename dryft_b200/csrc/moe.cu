@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
 }
 
 constexpr int ROWS_THREADS = 128;
-constexpr int ROWS_PER_BLOCK = 32;   // output features a block computes (8 per warp)
+constexpr int ROWS_PER_BLOCK = 8;    // output features a block computes (2 per warp): many small blocks keep enough loads in flight
 
 template <typename T>
 __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
@@ -116,38 +116,56 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
   const int o0 = blockIdx.y * ROWS_PER_BLOCK;
   constexpr int V = 16 / sizeof(T);
   const bool vec = (K % V) == 0;
-  for (int o = o0 + warp; o < min(o0 + ROWS_PER_BLOCK, n_out); o += ROWS_THREADS / 32) {
-    float d0 = 0.f, d1 = 0.f;
-    const T* r0 = we + (size_t)o * K;
-    const T* r1 = we + (size_t)(n_out + o) * K;   // mode 0: the matching up row
+  const int o_end = min(o0 + ROWS_PER_BLOCK, n_out);
+  // a warp takes two output features at a time: all their weight vectors are requested before any is used
+  for (int o = o0 + 2 * warp; o < o_end; o += 2 * (ROWS_THREADS / 32)) {
+    const bool two = o + 1 < o_end;
+    float d[2][2] = {{0.f, 0.f}, {0.f, 0.f}};    // [feature][gate | up]
+    const T* r[2][2];
+#pragma unroll
+    for (int f = 0; f < 2; ++f) {
+      r[f][0] = we + (size_t)(o + (two ? f : 0)) * K;
+      r[f][1] = we + (size_t)(n_out + o + (two ? f : 0)) * K;   // mode 0: the matching up row
+    }
     if (vec) {
+#pragma unroll 2
       for (int c = lane * V; c < K; c += 32 * V) {
+        uint4 wv[2][2];
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+          wv[f][0] = *reinterpret_cast<const uint4*>(r[f][0] + c);
+          if (mode == 0) wv[f][1] = *reinterpret_cast<const uint4*>(r[f][1] + c);
+        }
         const uint4 xv = *reinterpret_cast<const uint4*>(xs + c);
-        const uint4 w0 = *reinterpret_cast<const uint4*>(r0 + c);
         const T* xe = reinterpret_cast<const T*>(&xv);
-        const T* e0 = reinterpret_cast<const T*>(&w0);
 #pragma unroll
-        for (int t = 0; t < V; ++t) d0 = fmaf(to_f32<T>(e0[t]), to_f32<T>(xe[t]), d0);
-        if (mode == 0) {
-          const uint4 w1 = *reinterpret_cast<const uint4*>(r1 + c);
-          const T* e1 = reinterpret_cast<const T*>(&w1);
+        for (int f = 0; f < 2; ++f) {
+          const T* e0 = reinterpret_cast<const T*>(&wv[f][0]);
 #pragma unroll
-          for (int t = 0; t < V; ++t) d1 = fmaf(to_f32<T>(e1[t]), to_f32<T>(xe[t]), d1);
+          for (int t = 0; t < V; ++t) d[f][0] = fmaf(to_f32<T>(e0[t]), to_f32<T>(xe[t]), d[f][0]);
+          if (mode == 0) {
+            const T* e1 = reinterpret_cast<const T*>(&wv[f][1]);
+#pragma unroll
+            for (int t = 0; t < V; ++t) d[f][1] = fmaf(to_f32<T>(e1[t]), to_f32<T>(xe[t]), d[f][1]);
+          }
         }
       }
     } else {
       for (int c = lane; c < K; c += 32) {
         const float xv = to_f32<T>(xs[c]);
-        d0 = fmaf(to_f32<T>(r0[c]), xv, d0);
-        if (mode == 0) d1 = fmaf(to_f32<T>(r1[c]), xv, d1);
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+          d[f][0] = fmaf(to_f32<T>(r[f][0][c]), xv, d[f][0]);
+          if (mode == 0) d[f][1] = fmaf(to_f32<T>(r[f][1][c]), xv, d[f][1]);
+        }
       }
     }
-    d0 = warp_sum(d0);
-    if (mode == 0) {
-      d1 = warp_sum(d1);
-      d0 = d0 / (1.f + expf(-d0)) * d1;
+#pragma unroll
+    for (int f = 0; f < 2; ++f) {
+      float v = warp_sum(d[f][0]);
+      if (mode == 0) v = v / (1.f + expf(-v)) * warp_sum(d[f][1]);
+      if (lane == 0 && (f == 0 || two)) out[(size_t)a * n_out + o + f] = from_f32<T>(v);
     }
-    if (lane == 0) out[(size_t)a * n_out + o] = from_f32<T>(d0);
   }
 }
 

@@ -7,21 +7,22 @@
 //                  (expert, first sorted place) that the products walk, and their number.  One block.
 //   moe_grouped<0> act[p, f] = silu(Wg_e[f] . h[token(p)]) * (Wu_e[f] . h[token(p)])   rows gathered through perm
 //   moe_grouped<1> y[perm[p], c] = Wd_e[c] . act[p]                                   rows scattered back
-// A block computes 64 sorted rows of one expert x 64 output columns: 4 warps of 16 rows, mma.sync.m16n8k16 (bf16 in,
-// fp32 accumulate), operands through a two-stage cp.async ring of 64-wide k slices, rows and slices that do not exist
-// filled with zeros on their way in.  Inner sizes are multiples of 16.
+// A block of four warps computes 64 or 128 sorted rows of one expert x 128 weight rows (64 columns of gate and of up, or
+// 128 columns of down), a warp a quarter of it, with mma.sync.m16n8k16 (bf16 in, fp32 accumulate); operands through a
+// four-stage cp.async ring of 32-wide k slices, rows and slices that do not exist filled with zeros on their way in.
+// Inner sizes are multiples of 16.
 //
-// The grid is sized for the largest number of row tiles there can be (ceil(A/64) + E); blocks beyond the actual number
-// return at once.  No block waits on another block.
+// The grid is sized for the largest number of row tiles there can be (ceil(A/rows per tile) + E); blocks beyond the actual
+// number return at once.  No block waits on another block.
 #include "common.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int BM = 64, BN = 64, BK = 64;
-constexpr int THREADS = 128;
-constexpr int LDS = BK + 8;   // padded row stride (elements)
-constexpr int NT = BN / 8;
+constexpr int BK = 32;
+constexpr int LDS = BK + 8;   // padded row stride (elements): 80 bytes, conflict-free ldmatrix
+constexpr int STAGES = 4;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -46,7 +47,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 constexpr int SORT_THREADS = 1024;
 
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(
-    const int* __restrict__ idx, int n_assign, int E, int* __restrict__ offsets, int* __restrict__ perm,
+    const int* __restrict__ idx, int n_assign, int E, int BM, int* __restrict__ offsets, int* __restrict__ perm,
     int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ n_tiles) {
   extern __shared__ int sh[];   // counts[E], cursor[E]
   int* counts = sh;
@@ -76,15 +77,20 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(
 
 // MODE 0: A rows are h[perm[p] / top], B is W_gu[e] ([2F, K]: gate rows then up rows), out is act[p, F]
 // MODE 1: A rows are act[p],           B is W_d[e]  ([C, K]),                        out is y[perm[p], C]
-template <int MODE>
-__global__ void __launch_bounds__(THREADS) moe_grouped_kernel(
+// A block of 2 x 2 warps computes BM sorted rows x BN output columns (of gate AND up in mode 0), a warp BM/2 x BN/2.
+template <int MODE, int BM, int BN>
+__global__ void __launch_bounds__(128) moe_grouped_kernel(
     const bf16* __restrict__ a_in, const bf16* __restrict__ w, const int* __restrict__ offsets, const int* __restrict__ perm,
     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int top, int K,
     int n_out, bf16* __restrict__ out) {
-  constexpr int NB = MODE == 0 ? 2 * BN : BN;   // weight rows a block reads per k slice
+  constexpr int NTHREADS = 128;
+  constexpr int NMAT = MODE == 0 ? 2 : 1;       // weight matrices multiplied at once (gate and up)
+  constexpr int NB = NMAT * BN;                 // weight rows a block reads per k slice
+  constexpr int WM = BM / 2, WN = BN / 2;       // a warp's rows and columns
+  constexpr int MT = WM / 16, NT = WN / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // [2][BM][LDS]
-  bf16* bs = as + 2 * BM * LDS;                   // [2][NB][LDS]
+  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // [STAGES][BM][LDS]
+  bf16* bs = as + STAGES * BM * LDS;              // [STAGES][NB][LDS]
   __shared__ int row_src[BM];
 
   const int tile = blockIdx.x;
@@ -93,23 +99,24 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_kernel(
   const int rows = min(BM, offsets[e + 1] - p0);
   const int n0 = blockIdx.y * BN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 1, wn = warp & 1;
   const int g = lane >> 2, t = lane & 3;
 
-  if (tid < BM) row_src[tid] = tid < rows ? (MODE == 0 ? perm[p0 + tid] / top : p0 + tid) : -1;
+  for (int r = tid; r < BM; r += NTHREADS) row_src[r] = r < rows ? (MODE == 0 ? perm[p0 + r] / top : p0 + r) : -1;
   __syncthreads();
-  const bf16* we = w + (size_t)e * (MODE == 0 ? 2 * n_out : n_out) * K;
+  const bf16* we = w + (size_t)e * (NMAT * n_out) * K;
 
   auto load = [&](int stage, int k0) {
     bf16* a_st = as + stage * BM * LDS;
     bf16* b_st = bs + stage * NB * LDS;
     constexpr int CPR = BK / 8;
-    for (int i = tid; i < BM * CPR; i += THREADS) {
+    for (int i = tid; i < BM * CPR; i += NTHREADS) {
       const int r = i / CPR, c = i % CPR;
       const int src = row_src[r];
       const bool ok = src >= 0 && k0 + c * 8 < K;
       cp_async16(a_st + r * LDS + c * 8, a_in + (ok ? (size_t)src * K + k0 + c * 8 : 0), ok ? 16 : 0);
     }
-    for (int i = tid; i < NB * CPR; i += THREADS) {
+    for (int i = tid; i < NB * CPR; i += NTHREADS) {
       const int r = i / CPR, c = i % CPR;
       int wr = n0 + (r % BN);
       const bool ok = wr < n_out && k0 + c * 8 < K;
@@ -118,94 +125,117 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_kernel(
     }
   };
 
-  float acc[MODE == 0 ? 2 : 1][NT][4];
+  float acc[NMAT][MT][NT][4];
 #pragma unroll
-  for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m)
+  for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+    for (int i = 0; i < MT; ++i)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[m][i][j][x] = 0.f;
 
+  // a ring of STAGES k slices: slice s + STAGES - 1 is requested while slice s is multiplied; one group is committed per
+  // step whether or not it holds a slice, so that the number of groups in flight names the slice that has landed
   const int nk = (K + BK - 1) / BK;
-  load(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nk) load(s, s * BK);
+    cp_async_commit();
+  }
   for (int ks = 0; ks < nk; ++ks) {
-    const int stage = ks & 1;
-    if (ks + 1 < nk) {
-      load(stage ^ 1, (ks + 1) * BK);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const bf16* a_st = as + stage * BM * LDS;
-    const bf16* b_st = bs + stage * NB * LDS;
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();   // slice ks has landed for every thread, and every warp is done with the stage refilled next
+    if (ks + STAGES - 1 < nk) load((ks + STAGES - 1) % STAGES, (ks + STAGES - 1) * BK);
+    cp_async_commit();
+    const bf16* a_st = as + (ks % STAGES) * BM * LDS;
+    const bf16* b_st = bs + (ks % STAGES) * NB * LDS;
 #pragma unroll
     for (int kk = 0; kk < BK / 16; ++kk) {
-      unsigned a0, a1, a2, a3;
-      ldsm_x4(a0, a1, a2, a3, a_st + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+      unsigned a[MT][4];
 #pragma unroll
-      for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m) {
+      for (int i = 0; i < MT; ++i)
+        ldsm_x4(a[i][0], a[i][1], a[i][2], a[i][3], a_st + (wm * WM + i * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
           unsigned b0, b1, b2, b3;
-          ldsm_x4(b0, b1, b2, b3, b_st + (m * BN + j * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
-          mma16816(acc[m][j], a0, a1, a2, a3, b0, b1);
-          mma16816(acc[m][j + 1], a0, a1, a2, a3, b2, b3);
+          ldsm_x4(b0, b1, b2, b3, b_st + (m * BN + wn * WN + j * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+          for (int i = 0; i < MT; ++i) {
+            mma16816(acc[m][i][j], a[i][0], a[i][1], a[i][2], a[i][3], b0, b1);
+            mma16816(acc[m][i][j + 1], a[i][0], a[i][1], a[i][2], a[i][3], b2, b3);
+          }
         }
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
 
-  const int r0 = warp * 16 + g, r1 = r0 + 8;
-  size_t o0 = 0, o1 = 0;
-  if (MODE == 0) {
-    o0 = (size_t)(p0 + r0) * n_out;
-    o1 = (size_t)(p0 + r1) * n_out;
-  } else {
-    if (r0 < rows) o0 = (size_t)perm[p0 + r0] * n_out;
-    if (r1 < rows) o1 = (size_t)perm[p0 + r1] * n_out;
-  }
 #pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int c = n0 + j * 8 + 2 * t;
-    if (c >= n_out) continue;     // n_out is even (a multiple of 16): c + 1 is inside too
-    float v0 = acc[0][j][0], v1 = acc[0][j][1], v2 = acc[0][j][2], v3 = acc[0][j][3];
+  for (int i = 0; i < MT; ++i) {
+    const int r0 = wm * WM + i * 16 + g, r1 = r0 + 8;
+    size_t o0 = 0, o1 = 0;
     if (MODE == 0) {
-      v0 = v0 / (1.f + expf(-v0)) * acc[MODE == 0 ? 1 : 0][j][0];
-      v1 = v1 / (1.f + expf(-v1)) * acc[MODE == 0 ? 1 : 0][j][1];
-      v2 = v2 / (1.f + expf(-v2)) * acc[MODE == 0 ? 1 : 0][j][2];
-      v3 = v3 / (1.f + expf(-v3)) * acc[MODE == 0 ? 1 : 0][j][3];
+      o0 = (size_t)(p0 + r0) * n_out;
+      o1 = (size_t)(p0 + r1) * n_out;
+    } else {
+      if (r0 < rows) o0 = (size_t)perm[p0 + r0] * n_out;
+      if (r1 < rows) o1 = (size_t)perm[p0 + r1] * n_out;
     }
-    if (r0 < rows) *reinterpret_cast<unsigned*>(out + o0 + c) = pack_bf16(v0, v1);
-    if (r1 < rows) *reinterpret_cast<unsigned*>(out + o1 + c) = pack_bf16(v2, v3);
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int c = n0 + wn * WN + j * 8 + 2 * t;
+      if (c >= n_out) continue;     // n_out is even (a multiple of 16): c + 1 is inside too
+      float v0 = acc[0][i][j][0], v1 = acc[0][i][j][1], v2 = acc[0][i][j][2], v3 = acc[0][i][j][3];
+      if (MODE == 0) {
+        v0 = v0 / (1.f + expf(-v0)) * acc[NMAT - 1][i][j][0];
+        v1 = v1 / (1.f + expf(-v1)) * acc[NMAT - 1][i][j][1];
+        v2 = v2 / (1.f + expf(-v2)) * acc[NMAT - 1][i][j][2];
+        v3 = v3 / (1.f + expf(-v3)) * acc[NMAT - 1][i][j][3];
+      }
+      if (r0 < rows) *reinterpret_cast<unsigned*>(out + o0 + c) = pack_bf16(v0, v1);
+      if (r1 < rows) *reinterpret_cast<unsigned*>(out + o1 + c) = pack_bf16(v2, v3);
+    }
   }
 }
 
-template <int MODE> constexpr size_t gemm_smem() { return sizeof(bf16) * (size_t)LDS * 2 * (BM + (MODE == 0 ? 2 * BN : BN)); }
-
-template <int MODE>
+template <int MODE, int BM, int BN>
 int gemm_launch(const void* a_in, const void* w, const int* offsets, const int* perm, const int* tile_expert, const int* tile_row0,
                 const int* n_tiles, int top, int K, int n_out, void* out, int max_tiles, cudaStream_t st) {
   static bool attr_set = false;   // set by the first (eager) launch, outside any stream capture
-  const size_t smem = gemm_smem<MODE>();
+  constexpr size_t smem = sizeof(bf16) * (size_t)LDS * STAGES * (BM + (MODE == 0 ? 2 * BN : BN));
   if (smem > 48 * 1024 && !attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<MODE, BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   const int n_tiles_n = (n_out + BN - 1) / BN;
   if (n_tiles_n > 65535) return DRYFT_ERR_UNSUPPORTED;
   dim3 grid(max_tiles, n_tiles_n);
-  moe_grouped_kernel<MODE><<<grid, THREADS, smem, st>>>((const bf16*)a_in, (const bf16*)w, offsets, perm, tile_expert, tile_row0,
-                                                       n_tiles, top, K, n_out, (bf16*)out);
+  moe_grouped_kernel<MODE, BM, BN><<<grid, 128, smem, st>>>((const bf16*)a_in, (const bf16*)w, offsets, perm, tile_expert,
+                                                          tile_row0, n_tiles, top, K, n_out, (bf16*)out);
   return launch_status();
+}
+
+// rows per tile: 128 once an expert gets about a hundred rows on average (the weights are then re-read from L2 half as
+// often), 64 below that (fewer rows of padding per expert)
+inline int tile_rows_for(int n_assign, int E) {
+  static int forced = -1;   // DRYFT_MOE_TILE_ROWS=64|128 pins the choice (measurements)
+  if (forced < 0) {
+    const char* v = getenv("DRYFT_MOE_TILE_ROWS");
+    forced = v ? atoi(v) : 0;
+  }
+  if (forced == 64 || forced == 128) return forced;
+  return n_assign / E >= 96 ? 128 : 64;
 }
 }  // namespace
 
-DRYFT_API int dryft_moe_grouped_max_tiles(int n_assign, int E) { return (n_assign + BM - 1) / BM + E; }
+DRYFT_API int dryft_moe_grouped_max_tiles(int n_assign, int E) {
+  const int bm = tile_rows_for(n_assign, E);
+  return (n_assign + bm - 1) / bm + E;
+}
 
 // ints the caller provides in `work`: offsets[E+1] | perm[n_assign] | tile_expert[max_tiles] | tile_row0[max_tiles] | n_tiles[1]
 DRYFT_API long long dryft_moe_grouped_work_ints(int n_assign, int E) {
@@ -226,10 +256,16 @@ DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void
   int* tile_expert = perm + n_assign;
   int* tile_row0 = tile_expert + max_tiles;
   int* n_tiles = tile_row0 + max_tiles;
-  moe_sort_kernel<<<1, SORT_THREADS, sizeof(int) * 2 * E, st>>>(idx, n_assign, E, offsets, perm, tile_expert, tile_row0, n_tiles);
+  const int bm = tile_rows_for(n_assign, E);
+  moe_sort_kernel<<<1, SORT_THREADS, sizeof(int) * 2 * E, st>>>(idx, n_assign, E, bm, offsets, perm, tile_expert, tile_row0, n_tiles);
   int rc = launch_status();
   if (rc) return rc;
-  rc = gemm_launch<0>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+  if (bm == 128) {
+    rc = gemm_launch<0, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+    if (rc) return rc;
+    return gemm_launch<1, 128, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
+  }
+  rc = gemm_launch<0, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
   if (rc) return rc;
-  return gemm_launch<1>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
+  return gemm_launch<1, 64, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
 }

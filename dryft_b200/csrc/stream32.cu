@@ -39,14 +39,60 @@ __global__ void __launch_bounds__(THREADS) embed_sinusoid_kernel(
   }
 }
 
+// four consecutive elements at once (8 or 16 bytes); rows whose width is not a multiple of four go element by element
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS) stream_norm_add_kernel(
     const T* __restrict__ y, const float* __restrict__ wts, int top, const float* __restrict__ w, float offset, float eps,
     float* __restrict__ x32, T* __restrict__ h, int width) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float scratch[33];
   const int n = blockIdx.x;
   float ss = 0.f;
+  if ((width & 3) == 0) {
+    for (int c = threadIdx.x * 4; c < width; c += THREADS * 4) {
+      float4 v;
+      if (top > 0) {
+        v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < top; ++k) {
+          const float wk = wts[(size_t)n * top + k];
+          const float4 u = load4<T>(y + ((size_t)n * top + k) * width + c);
+          v.x = fmaf(wk, u.x, v.x); v.y = fmaf(wk, u.y, v.y); v.z = fmaf(wk, u.z, v.z); v.w = fmaf(wk, u.w, v.w);
+        }
+      } else {
+        v = load4<T>(y + (size_t)n * width + c);
+      }
+      *reinterpret_cast<float4*>(row + c) = v;
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x * 4; c < width; c += THREADS * 4) {
+      const float4 r = *reinterpret_cast<const float4*>(row + c), ww = *reinterpret_cast<const float4*>(w + c);
+      float4 v = *reinterpret_cast<const float4*>(x32 + (size_t)n * width + c);
+      v.x += r.x * inv * (offset + ww.x); v.y += r.y * inv * (offset + ww.y);
+      v.z += r.z * inv * (offset + ww.z); v.w += r.w * inv * (offset + ww.w);
+      *reinterpret_cast<float4*>(x32 + (size_t)n * width + c) = v;
+      if (h) store4<T>(h + (size_t)n * width + c, v);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < width; c += THREADS) {
     float v;
     if (top > 0) {
@@ -71,7 +117,7 @@ template <typename TI, typename T>
 __global__ void __launch_bounds__(THREADS) stream_norm_rows_kernel(
     const TI* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w, float offset, float eps,
     T* __restrict__ out, int width) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;

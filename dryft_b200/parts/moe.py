@@ -6,8 +6,8 @@ neighbours, a group scores its largest member, and only experts of the ``keep`` 
 largest scores among those are the token's experts, weighted by their scores ``s`` as they are (or divided by their sum
 with ``renormalize``).  The output is the weighted sum of the chosen experts' outputs.
 
-The router's product runs in 32-bit on the activations as the layer hands them over (``csrc/gemm_f32.cu``); the choice
-is ``csrc/moe.cu:moe_route``.  The experts run assignment by assignment for few tokens and in the 32-bit path
+The router's product leaves 32-bit logits (32-bit accumulation over the activations as the layer hands them over); the
+choice is ``csrc/moe.cu:moe_route``.  The experts run assignment by assignment for few tokens and in the 32-bit path
 (``csrc/moe.cu:moe_rows``: every chosen expert's weights are read once per assignment), and as grouped tensor-core
 products over the tokens sorted by expert for prompts in bfloat16 (``csrc/moe_grouped.cu``).  The weighted sum is left
 to the caller through ``forward_parts`` (a layer that normalises the sum forms it inside its norm kernel in 32-bit);
@@ -22,6 +22,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import Runtime, StepContext, TensorInfo, register_ffn
+from .linear import linear
 
 _ROLES = {"router": "router.weight", "expert": "experts.{}.", "gate": "gate_proj.weight", "up": "up_proj.weight",
           "down": "down_proj.weight"}
@@ -58,8 +59,10 @@ class MoE:
         if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
             raise ValueError(f"moe: {self.experts} experts, {self.groups} groups, keep {self.keep}, top {self.top} do not go together")
         nm = _names(params)
-        # the router always runs in 32-bit: its weight is widened once here
-        self.w_router = weights.load(prefix + nm["router"], "matrix").to(torch.float32).contiguous()
+        # The router's logits are 32-bit sums.  In the bfloat16 path its operands are the bfloat16 activations and the
+        # weight as stored (their products are exact in 32-bit), multiplied by the tensor-core products with 32-bit
+        # accumulation and a 32-bit result; in the 32-bit path everything is float32.
+        self.w_router = weights.load(prefix + nm["router"], "matrix")
         gu, dn = [], []
         for i in range(self.experts):
             ep = prefix + nm["expert"].format(i)
@@ -78,8 +81,7 @@ class MoE:
     def route(self, h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Chosen experts ``[n, top]`` int32 and their weights ``[n, top]`` float32."""
         n = h.shape[0]
-        logits = torch.empty((n, self.experts), dtype=torch.float32, device=h.device)
-        K.gemm_nt_f32(h if h.dtype == torch.float32 else h.to(torch.float32), self.w_router, logits)
+        logits = linear(h, self.w_router, self.rt, out_dtype=torch.float32)
         idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
         K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)
