@@ -4,7 +4,8 @@
 //                 neighbours; a group scores its largest member; only experts of the `keep` best groups can be chosen
 //                 (n_groups = keep = 1: no groups).  The `top` allowed experts with the largest scores are chosen;
 //                 their weights are the scores themselves, or the scores divided by their sum (`renorm`).
-//                 Ties go to the lower index.  One warp per token.
+//                 Ties go to the lower index.  One warp per token.  moe_route_rows is the same for few tokens with the
+//                 router's product inside (one block per token, one launch instead of two).
 //   moe_rows      an assignment a = (token, k) multiplies its token's activation row by its expert's matrices, every
 //                 weight row read once per assignment (a matrix-vector product per warp row): the form for few
 //                 tokens (decode) and for the 32-bit path.
@@ -29,16 +30,10 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
-    const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
-    int* __restrict__ idx_out, float* __restrict__ w_out) {
-  extern __shared__ float sm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * ROUTE_WARPS + warp;
-  if (n >= n_tokens) return;
-  float* s = sm + (size_t)warp * (E + n_groups);   // scores; an expert that may no longer be chosen is set to -1
-  float* gs = s + E;                               // group scores
-  const float* z = logits + (size_t)n * E;
+// One warp's choice for one token: z holds the E logits (global or shared memory), s and gs are the warp's scratch
+// ([E] scores, [n_groups] group scores) in shared memory.
+__device__ __forceinline__ void route_one(const float* z, float* s, float* gs, int lane, int n, int E, int n_groups, int keep,
+                                          int top, int renorm, int* __restrict__ idx_out, float* __restrict__ w_out) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -93,6 +88,53 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
   }
   if (renorm && lane == 0 && wsum > 0.f)
     for (int r = 0; r < top; ++r) w_out[(size_t)n * top + r] /= wsum;
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
+    const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
+    int* __restrict__ idx_out, float* __restrict__ w_out) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * ROUTE_WARPS + warp;
+  if (n >= n_tokens) return;
+  float* s = sm + (size_t)warp * (E + n_groups);
+  route_one(logits + (size_t)n * E, s, s + E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
+}
+
+// Few tokens (decode): the router's product and its choice in one launch.  One block per token: the token's row is staged
+// in shared memory, every warp takes experts in turn (z_e = W_router[e] . h, 32-bit accumulation), warp 0 then chooses.
+constexpr int ROUTE_ROW_THREADS = 1024;   // 32 warps: one or two experts a warp keeps the block one or two trips to memory long
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_ROW_THREADS) moe_route_rows_kernel(
+    const T* __restrict__ h, const T* __restrict__ w_router, int K, int E, int n_groups, int keep, int top, int renorm,
+    int* __restrict__ idx_out, float* __restrict__ w_out) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  T* xs = reinterpret_cast<T*>(smraw);                  // the token's row
+  float* z = reinterpret_cast<float*>(smraw + (sizeof(T) * (size_t)K + 15) / 16 * 16);   // [E] logits, [E] scores, [n_groups]
+  const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int c = threadIdx.x; c < K; c += ROUTE_ROW_THREADS) xs[c] = h[(size_t)n * K + c];
+  __syncthreads();
+  for (int e = warp; e < E; e += ROUTE_ROW_THREADS / 32) {
+    const T* wr = w_router + (size_t)e * K;
+    float d = 0.f;
+    constexpr int V = 16 / sizeof(T);
+    if (K % V == 0) {
+#pragma unroll 4
+      for (int c = lane * V; c < K; c += 32 * V) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wr + c), xv = *reinterpret_cast<const uint4*>(xs + c);
+        const T* we = reinterpret_cast<const T*>(&wv);
+        const T* xe = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+        for (int t = 0; t < V; ++t) d = fmaf(to_f32<T>(we[t]), to_f32<T>(xe[t]), d);
+      }
+    } else {
+      for (int c = lane; c < K; c += 32) d = fmaf(to_f32<T>(wr[c]), to_f32<T>(xs[c]), d);
+    }
+    d = warp_sum(d);
+    if (lane == 0) z[e] = d;
+  }
+  __syncthreads();
+  if (warp == 0) route_one(z, z + E, z + 2 * E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
 }
 
 constexpr int ROWS_THREADS = 128;
@@ -222,5 +264,20 @@ DRYFT_API int dryft_moe_combine(int is_bf16, const void* y, const float* wts, in
     moe_combine_kernel<__nv_bfloat16><<<n, 256, 0, st>>>((const __nv_bfloat16*)y, wts, top, width, (__nv_bfloat16*)out);
   else
     moe_combine_kernel<float><<<n, 256, 0, st>>>((const float*)y, wts, top, width, (float*)out);
+  return launch_status();
+}
+
+DRYFT_API int dryft_moe_route_rows(int is_bf16, const void* h, const void* w_router, int n_tokens, int K, int E, int n_groups,
+                                   int keep, int top, int renorm, int* idx_out, float* w_out, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || K < 1) return DRYFT_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(float) * (size_t)(2 * E + n_groups) + ((is_bf16 ? 2 : 4) * (size_t)K + 15) / 16 * 16;
+  if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (is_bf16)
+    moe_route_rows_kernel<__nv_bfloat16><<<n_tokens, ROUTE_ROW_THREADS, smem, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)w_router,
+                                                                                    K, E, n_groups, keep, top, renorm, idx_out, w_out);
+  else
+    moe_route_rows_kernel<float><<<n_tokens, ROUTE_ROW_THREADS, smem, st>>>((const float*)h, (const float*)w_router, K, E, n_groups, keep,
+                                                                            top, renorm, idx_out, w_out);
   return launch_status();
 }

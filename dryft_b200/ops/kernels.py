@@ -71,11 +71,12 @@ def core() -> ctypes.CDLL:
             lib.dryft_moe_route.argtypes = [_p, _i, _i, _i, _i, _i, _i, _p, _p, _p]
             lib.dryft_moe_rows.argtypes = [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _p]
             lib.dryft_moe_combine.argtypes = [_i, _p, _p, _i, _i, _p, _i, _p]
+            lib.dryft_moe_route_rows.argtypes = [_i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
                          "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store", "dryft_rope_table",
                          "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq",
                          "dryft_embed_sinusoid", "dryft_stream_norm_add", "dryft_stream_norm_rows", "dryft_kv_maps_store",
-                         "dryft_moe_route", "dryft_moe_rows", "dryft_moe_combine"):
+                         "dryft_moe_route", "dryft_moe_rows", "dryft_moe_combine", "dryft_moe_route_rows"):
                 getattr(lib, name).restype = _i
             _core = lib
         return _core
@@ -744,6 +745,23 @@ def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm
     _need(w_out, "w_out", torch.float32, (n, top))
     _ok(core().dryft_moe_route(_ptr(logits), n, e, int(n_groups), int(keep), int(top), int(renorm), _ptr(idx_out), _ptr(w_out),
                                _stream()), f"moe_route ({e} experts, {n_groups} groups, keep {keep}, top {top})")
+
+
+def moe_route_rows_supported(hidden: int, experts: int, groups: int, itemsize: int) -> bool:
+    """Whether the one-launch router (product and choice) takes these sizes: its row and scores fit 48 KB of shared memory."""
+    return 4 * (2 * experts + groups) + (itemsize * hidden + 15) // 16 * 16 <= 48 * 1024
+
+
+def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False) -> None:
+    """``moe_route`` of ``logits = h @ w_router.T`` (32-bit sums) in one launch, for few tokens: one block per token."""
+    n, k = h.shape
+    e = w_router.shape[0]
+    _need(h, "h")
+    _need(w_router, "router weight", h.dtype, (e, k))
+    _need(idx_out, "idx_out", torch.int32, (n, top))
+    _need(w_out, "w_out", torch.float32, (n, top))
+    _ok(core().dryft_moe_route_rows(_act(h, "h"), _ptr(h), _ptr(w_router), n, k, e, int(n_groups), int(keep), int(top), int(renorm),
+                                    _ptr(idx_out), _ptr(w_out), _stream()), f"moe_route_rows ({e} experts over {k})")
 
 
 def moe_rows(a, w, idx, out, mode: str) -> None:

@@ -77,13 +77,20 @@ class MoE:
             K.moe_grouped_lib()
 
     GROUPED_MIN_TOKENS = 32   # below this every assignment streams its expert's weights itself
+    ROUTE_ROWS_MAX = 16       # up to this many tokens the router's product and choice are one launch ...
+    ROUTE_ROWS_MAX_WEIGHTS = 64 * 1024   # ... while one block can stream the router's weight quickly enough (measured: 32 x 1,024
+                                         # gains a launch, 64 x 2,048 takes longer than the two launches it replaces)
 
     def route(self, h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Chosen experts ``[n, top]`` int32 and their weights ``[n, top]`` float32."""
         n = h.shape[0]
-        logits = linear(h, self.w_router, self.rt, out_dtype=torch.float32)
         idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
+        if (n <= self.ROUTE_ROWS_MAX and self.w_router.dtype == h.dtype and self.w_router.numel() <= self.ROUTE_ROWS_MAX_WEIGHTS
+                and K.moe_route_rows_supported(self.hidden, self.experts, self.groups, h.element_size())):
+            K.moe_route_rows(h, self.w_router, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)   # one launch
+            return idx, wts
+        logits = linear(h, self.w_router, self.rt, out_dtype=torch.float32)
         K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)
         return idx, wts
 

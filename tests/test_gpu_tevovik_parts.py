@@ -203,6 +203,20 @@ def test_router_choice(E, groups, keep, top):
 
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,groups,keep,top,width", [(8, 4, 2, 2, 48), (6, 1, 1, 1, 72), (64, 8, 4, 8, 1024), (12, 3, 3, 4, 101)])
+def test_router_product_and_choice_in_one_launch(act, E, groups, keep, top, width):
+    n = 13
+    h = torch.randn(n, width).to(act)
+    w = (torch.randn(E, width) / math.sqrt(width) * 3).to(act)
+    idx = torch.empty(n, top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n, top, dtype=torch.float32, device=DEV)
+    K().moe_route_rows(h.to(DEV), w.to(DEV), groups, keep, top, idx, wts)
+    want_idx, want_w = P.route(h.double(), w.double(), {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}})
+    assert (idx.cpu().long().sort(-1).values == want_idx.sort(-1).values).all()
+    close(wts.sort(-1).values, want_w.sort(-1).values, 1e-5, "weights")
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,width,ff,E,top", [(5, 48, 40, 8, 2), (1, 72, 24, 6, 1), (70, 64, 56, 12, 4), (300, 128, 96, 16, 3)])
 def test_experts_assignment_by_assignment_and_grouped(act, n, width, ff, E, top):
     kern = K()
