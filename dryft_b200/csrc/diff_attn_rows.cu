@@ -274,6 +274,7 @@ __global__ void __launch_bounds__(THREADS) diff_attn_reduce_kernel(
 #pragma unroll
     for (int m = 0; m < MAPS; ++m) {
       float num = 0.f;
+#pragma unroll 4
       for (int s = 0; s < n_splits; ++s) num = fmaf(wgt[m * n_splits + s], part_o[((rh * MAPS + m) * n_splits + s) * DV + d], num);
       a[m] = num;
     }

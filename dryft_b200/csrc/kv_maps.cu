@@ -9,7 +9,7 @@
 // v_pages [pages, nKV, PAGE, DV] at the token's (slot, position).  Padding tokens (slot < 0) write nothing but
 // zero queries.
 //
-// One block per token, one warp per vector in turn.  No block waits on another.
+// Blocks (token, share of the token's vectors), one warp per vector.  No block waits on another.
 #include "common.cuh"
 #include <math.h>
 
@@ -43,7 +43,9 @@ __global__ void __launch_bounds__(THREADS) kv_maps_store_kernel(
     krow = k_pages + (((size_t)page * nKV) * page_size + r) * (size_t)(maps * D);   // kv head g adds g * page_size * maps*D
     vrow = v_pages + (((size_t)page * nKV) * page_size + r) * (size_t)DV;
   }
-  for (int u = warp; u < nq + nk + nv; u += nwarp) {
+  // a warp takes one vector; the grid's second dimension covers a token's vectors, so that a step of few tokens (decode)
+  // is many short blocks instead of a few long ones
+  for (int u = blockIdx.y * nwarp + warp; u < nq + nk + nv; u += gridDim.y * nwarp) {
     if (u < nq + nk) {
       const bool is_q = u < nq;
       const int v = is_q ? u : u - nq;                 // vector index: head * maps + map
@@ -123,7 +125,9 @@ int launch(const void* proj, int stride, const float* q_w, const float* k_w, con
   if (n <= 0) return 0;
   if (nH < 1 || nKV < 1 || maps < 1 || D < 1 || DV < 1) return DRYFT_ERR_UNSUPPORTED;
   if (write_kv && (page_size < 1 || !k_pages || !v_pages || !page_table)) return DRYFT_ERR_UNSUPPORTED;
-  kv_maps_store_kernel<T><<<n, THREADS, 0, st>>>((const T*)proj, stride, q_w, k_w, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
+  const int units = nH * maps + (write_kv ? nKV * maps + nKV : 0);
+  dim3 grid(n, (unsigned)min(64, (units + THREADS / 32 - 1) / (THREADS / 32)));
+  kv_maps_store_kernel<T><<<grid, THREADS, 0, st>>>((const T*)proj, stride, q_w, k_w, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
                                                  (T*)v_pages, page_table, max_pages, nH, nKV, maps, D, DV, page_size, eps, write_kv);
   return launch_status();
 }

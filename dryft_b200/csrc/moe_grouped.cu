@@ -9,8 +9,9 @@
 //   moe_grouped<1> y[perm[p], c] = Wd_e[c] . act[p]                                   rows scattered back
 // A block of four warps computes 64 or 128 sorted rows of one expert x 128 weight rows (64 columns of gate and of up, or
 // 128 columns of down), a warp a quarter of it, with mma.sync.m16n8k16 (bf16 in, fp32 accumulate); operands through a
-// four-stage cp.async ring of 32-wide k slices, rows and slices that do not exist filled with zeros on their way in.
-// Inner sizes are multiples of 16.
+// cp.async ring of k slices (two stages of 64 by default: measured at 2,048 tokens x 8 of 64 experts of 768 x 2,048,
+// 230 TFLOP/s against 211 with three stages and 176 with four of 32 -- the blocks an SM holds matter more than the
+// ring's depth), rows and slices that do not exist filled with zeros on their way in.  Inner sizes are multiples of 16.
 //
 // The grid is sized for the largest number of row tiles there can be (ceil(A/rows per tile) + E); blocks beyond the actual
 // number return at once.  No block waits on another block.
@@ -20,9 +21,17 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int BK = 32;
-constexpr int LDS = BK + 8;   // padded row stride (elements): 80 bytes, conflict-free ldmatrix
-constexpr int STAGES = 4;
+#ifndef DRYFT_MOE_BK
+#define DRYFT_MOE_BK 64
+#endif
+#ifndef DRYFT_MOE_STAGES
+#define DRYFT_MOE_STAGES 2
+#endif
+constexpr int BK = DRYFT_MOE_BK;          // k slice: 32 or 64
+constexpr int LDS = BK + 8;               // padded row stride (elements): conflict-free ldmatrix
+constexpr int STAGES = DRYFT_MOE_STAGES;
+static_assert(BK == 32 || BK == 64, "k slices of 32 or 64");
+static_assert(STAGES >= 2 && STAGES <= 6, "two to six stages");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);

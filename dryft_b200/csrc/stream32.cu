@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(THREADS) stream_norm_add_kernel(
       float4 v;
       if (top > 0) {
         v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
         for (int k = 0; k < top; ++k) {
           const float wk = wts[(size_t)n * top + k];
           const float4 u = load4<T>(y + ((size_t)n * top + k) * width + c);

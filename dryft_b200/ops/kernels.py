@@ -109,8 +109,8 @@ def diff_attention_rows_lib(qk_dim: int, v_dim: int, group: int, page: int) -> c
     """The row-wise (decode / 32-bit) differential attention kernel compiled for these sizes."""
     if qk_dim <= 0 or v_dim <= 0 or 2 * qk_dim > 512 or v_dim > 512:
         raise KernelError(f"differential attention takes map sizes up to 256 and value sizes up to 512, got {qk_dim}, {v_dim}")
-    if group < 1 or group > 8:
-        raise KernelError(f"differential attention takes 1..8 query heads per kv head, got {group}")
+    if group < 1 or group > 32:
+        raise KernelError(f"differential attention takes 1..32 query heads per kv head, got {group}")
     key = ("diff_rows", qk_dim, v_dim, group, page)
     with _lock:
         lib = _variants.get(key)
@@ -868,7 +868,13 @@ def moe_grouped_lib() -> ctypes.CDLL:
     global _moe_grouped
     with _lock:
         if _moe_grouped is None:
-            lib = _load(build.build_library("moe_grouped", ("moe_grouped.cu",)))
+            import os
+
+            defs = {}   # measurement knobs: the ring's slice width and depth (the source's defaults otherwise)
+            for var, name in (("DRYFT_MOE_BK", "DRYFT_MOE_BK"), ("DRYFT_MOE_STAGES", "DRYFT_MOE_STAGES")):
+                if os.environ.get(var):
+                    defs[name] = int(os.environ[var])
+            lib = _load(build.build_library("moe_grouped", ("moe_grouped.cu",), defs))
             lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p]
             lib.dryft_moe_grouped.restype = _i
             lib.dryft_moe_grouped_work_ints.argtypes = [_i, _i]
