@@ -15,8 +15,9 @@
 // Scores, maxima, sums, the combination and its norm are 32-bit.
 //
 // Grid (rows, kv heads, splits).  One block serves the GROUP query heads of a kv head (2*GROUP maps) for one row over
-// a contiguous range of pages.  With one split the block finishes the row itself; otherwise it leaves un-normalised
-// partials (acc, m, l) per map and `diff_attn_reduce_kernel` combines them and applies the epilogue.
+// a contiguous range of pages.  With one split the block finishes the row itself; otherwise every block leaves its
+// un-normalised partials (acc, m, l) per map and draws a ticket, and the block that draws the last ticket of its
+// (row, kv head) combines the splits and applies the epilogue -- one launch either way.
 // No block waits on another block; there is no spin anywhere in this file.
 #include "common.cuh"
 #include <math.h>
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
     const T* __restrict__ gate, int gate_stride,                    // gate[n * gate_stride + h] (logits) or null
     T* __restrict__ out,                                            // [N, nH * DV]
     float* __restrict__ part_o, float* __restrict__ part_ml,        // [N, nH, 2, S, DV], [N, nH, 2, S, 2]
+    int* __restrict__ tickets,                                      // [N * nKV] zeros; left zero
     int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale) {
   using L = Smem<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -76,22 +78,17 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
   float* a_s = l_s + GM;
   float* ob = a_s + GM;                                   // [G][DV]
   float* ssq = ob + G * DV;                               // [G]
+  float* wgt = ssq + G;                                   // [GM][n_splits]: each split's share, for the block that combines
+  __shared__ int s_last;
 
   const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int nH = nKV * G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slot = tok_slot[n];
 
-  if (slot < 0) {  // padding row: defined zeros, no cache access
-    if (n_splits == 1) {
+  if (slot < 0) {  // padding row: defined zeros, no cache access, no ticket (every split of the row comes here)
+    if (split == 0)
       for (int i = tid; i < G * DV; i += THREADS) out[(size_t)n * nH * DV + (size_t)kvh * G * DV + i] = from_f32<T>(0.f);
-    } else {
-      for (int gm = 0; gm < GM; ++gm) {
-        const size_t pi = (((size_t)n * nH + kvh * G) * MAPS + gm) * n_splits + split;
-        for (int d = tid; d < DV; d += THREADS) part_o[pi * DV + d] = 0.f;
-        if (tid == 0) { part_ml[pi * 2] = -INFINITY; part_ml[pi * 2 + 1] = 0.f; }
-      }
-    }
     return;
   }
 
@@ -198,34 +195,91 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
   }
   __syncthreads();
   if (n_splits > 1) {
+    const size_t base = ((size_t)n * nH + kvh * G) * MAPS;   // first of this block's GM maps
 #pragma unroll
     for (int i = 0; i < DIMS_PER_THREAD; ++i) {
       const int d = tid + i * THREADS;
       if (d >= DV) continue;
 #pragma unroll
-      for (int gm = 0; gm < GM; ++gm)
-        part_o[((((size_t)n * nH + kvh * G) * MAPS + gm) * n_splits + split) * DV + d] = acc[i][gm];
+      for (int gm = 0; gm < GM; ++gm) part_o[((base + gm) * n_splits + split) * DV + d] = acc[i][gm];
     }
     if (tid < GM) {
-      const size_t pi = (((size_t)n * nH + kvh * G) * MAPS + tid) * n_splits + split;
+      const size_t pi = (base + tid) * n_splits + split;
       part_ml[pi * 2] = m_s[tid];
       part_ml[pi * 2 + 1] = l_s[tid];
     }
-    return;
-  }
-  // one split: combine the two maps, normalise over the value dims, gate, store
+    // The block that draws the last ticket of this (row, kv head) combines all splits; nobody waits.  Its reads of the
+    // other blocks' partials go to L2 (ld.global.cg) behind the fences.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int t = atomicAdd(&tickets[n * nKV + kvh], 1);
+      s_last = (t == n_splits - 1);
+      if (s_last) tickets[n * nKV + kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int gm = warp; gm < GM; gm += NWARP) {   // per map: w_s = exp(m_s - max m) / sum_s' exp(m_s' - max m) l_s'
+      const float* ml = part_ml + (base + gm) * n_splits * 2;
+      float mx = -INFINITY;
+      for (int sp = lane; sp < n_splits; sp += 32) mx = fmaxf(mx, __ldcg(ml + sp * 2));
+      mx = warp_max(mx);
+      float denom = 0.f;
+      for (int sp = lane; sp < n_splits; sp += 32) {
+        const float m = __ldcg(ml + sp * 2);
+        if (m != -INFINITY) denom += expf(m - mx) * __ldcg(ml + sp * 2 + 1);
+      }
+      denom = warp_sum(denom);
+      for (int sp = lane; sp < n_splits; sp += 32) {
+        const float m = __ldcg(ml + sp * 2);
+        wgt[gm * n_splits + sp] = (m != -INFINITY && denom > 0.f) ? expf(m - mx) / denom : 0.f;
+      }
+    }
+    __syncthreads();
+    // a thread owns the outputs tid, tid + THREADS, ...; per split all their partials are requested before any is used
+    constexpr int ITEMS = (G * DV + THREADS - 1) / THREADS;
+    float a[ITEMS][MAPS];
 #pragma unroll
-  for (int i = 0; i < DIMS_PER_THREAD; ++i) {
-    const int d = tid + i * THREADS;
-    if (d >= DV) continue;
+    for (int i = 0; i < ITEMS; ++i)
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float l1 = l_s[g * MAPS], l2 = l_s[g * MAPS + 1];
-      const float a1 = l1 > 0.f ? acc[i][g * MAPS] / l1 : 0.f;
-      const float a2 = l2 > 0.f ? acc[i][g * MAPS + 1] / l2 : 0.f;
-      ob[g * DV + d] = a1 - lambda * a2;
+      for (int m = 0; m < MAPS; ++m) a[i][m] = 0.f;
+#pragma unroll 2
+    for (int sp = 0; sp < n_splits; ++sp) {
+      float v[ITEMS][MAPS];
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int item = min(tid + i * THREADS, G * DV - 1);
+        const int g = item / DV, d = item % DV;
+#pragma unroll
+        for (int m = 0; m < MAPS; ++m) v[i][m] = __ldcg(part_o + ((base + g * MAPS + m) * n_splits + sp) * DV + d);
+      }
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = min(tid + i * THREADS, G * DV - 1) / DV;
+#pragma unroll
+        for (int m = 0; m < MAPS; ++m) a[i][m] = fmaf(wgt[(g * MAPS + m) * n_splits + sp], v[i][m], a[i][m]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+      if (tid + i * THREADS < G * DV) ob[tid + i * THREADS] = a[i][0] - lambda * a[i][1];
+  } else {
+    // one split: this block holds everything
+#pragma unroll
+    for (int i = 0; i < DIMS_PER_THREAD; ++i) {
+      const int d = tid + i * THREADS;
+      if (d >= DV) continue;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float l1 = l_s[g * MAPS], l2 = l_s[g * MAPS + 1];
+        const float a1 = l1 > 0.f ? acc[i][g * MAPS] / l1 : 0.f;
+        const float a2 = l2 > 0.f ? acc[i][g * MAPS + 1] / l2 : 0.f;
+        ob[g * DV + d] = a1 - lambda * a2;
+      }
     }
   }
+  // the two maps are combined in ob: normalise over the value dims, gate, store
   __syncthreads();
   for (int g = warp; g < G; g += NWARP) {
     float ss = 0.f;
@@ -242,63 +296,16 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
     out[((size_t)n * nH + (size_t)kvh * G) * DV + i] = from_f32<T>(ob[i] * ssq[i / DV]);
 }
 
-// Combine the partials of one (row, head): per map  w_s = exp(m_s - max m) / sum_s' w_s' l_s',  a = sum w_s acc_s ; then
-// the same epilogue as above.
-template <typename T>
-__global__ void __launch_bounds__(THREADS) diff_attn_reduce_kernel(
-    const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ tok_slot,
-    const T* __restrict__ gate, int gate_stride, T* __restrict__ out, int nH, int n_splits, float lambda, float sub_eps,
-    float out_scale) {
-  __shared__ float o_s[DV];
-  __shared__ float scratch[33];
-  extern __shared__ float wgt[];   // [MAPS][n_splits]: each split's share exp(m_s - max m) / sum, worked out once
-  const size_t rh = blockIdx.x;  // row * nH + head
-  const int n = (int)(rh / nH), h = (int)(rh % nH);
-  if (threadIdx.x < MAPS * 32) {   // one warp per map
-    const int m = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float* ml = part_ml + (rh * MAPS + m) * n_splits * 2;
-    float mx = -INFINITY;
-    for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, ml[s * 2]);
-    mx = warp_max(mx);
-    float denom = 0.f;
-    for (int s = lane; s < n_splits; s += 32)
-      if (ml[s * 2] != -INFINITY) denom += expf(ml[s * 2] - mx) * ml[s * 2 + 1];
-    denom = warp_sum(denom);
-    for (int s = lane; s < n_splits; s += 32)
-      wgt[m * n_splits + s] = (ml[s * 2] != -INFINITY && denom > 0.f) ? expf(ml[s * 2] - mx) / denom : 0.f;
-  }
-  __syncthreads();
-  float ss = 0.f;
-  for (int d = threadIdx.x; d < DV; d += THREADS) {
-    float a[MAPS];
-#pragma unroll
-    for (int m = 0; m < MAPS; ++m) {
-      float num = 0.f;
-#pragma unroll 4
-      for (int s = 0; s < n_splits; ++s) num = fmaf(wgt[m * n_splits + s], part_o[((rh * MAPS + m) * n_splits + s) * DV + d], num);
-      a[m] = num;
-    }
-    const float o = a[0] - lambda * a[1];
-    o_s[d] = o;
-    ss = fmaf(o, o, ss);
-  }
-  ss = block_sum(ss, scratch);
-  float f = out_scale / sqrtf(ss / (float)DV + sub_eps);
-  if (tok_slot[n] < 0) f = 0.f;
-  else if (gate) f *= 1.f / (1.f + expf(-to_f32<T>(gate[(size_t)n * gate_stride + h])));
-  for (int d = threadIdx.x; d < DV; d += THREADS) out[rh * DV + d] = from_f32<T>(o_s[d] * f);
-}
-
 template <typename T>
 int launch(const void* q, const void* k_pages, const void* v_pages, const int* page_table, int max_pages,
            const int* tok_slot, const int* tok_pos, const void* gate, int gate_stride, void* out, float* part_o, float* part_ml,
-           int n_rows, int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale,
+           int* tickets, int n_rows, int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale,
            cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 4096) return DRYFT_ERR_UNSUPPORTED;
-  if (n_splits > 1 && (!part_o || !part_ml)) return DRYFT_ERR_UNSUPPORTED;
-  const size_t smem = Smem<T>::bytes();
-  if (smem > 227 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
+  const size_t smem = Smem<T>::bytes() + sizeof(float) * (size_t)GM * n_splits;
+  if (smem > 224 * 1024) return DRYFT_ERR_UNSUPPORTED;   // the kernel's few static bytes count against the same 227 KB
   static bool attr_set[64] = {false};   // per instantiation and device; set by the first (eager) launch
   if (smem > 48 * 1024) {
     int dev = 0;
@@ -306,7 +313,8 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return DRYFT_ERR_UNSUPPORTED;
     if (!attr_set[dev]) {
-      e = cudaFuncSetAttribute(diff_attn_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      // the largest there is: the size grows with the split count, and the attribute is set once
+      e = cudaFuncSetAttribute(diff_attn_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
       if (e != cudaSuccess) return (int)e;
       attr_set[dev] = true;
     }
@@ -314,11 +322,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
   dim3 grid(n_rows, nKV, n_splits);
   diff_attn_rows_kernel<T><<<grid, THREADS, smem, st>>>((const T*)q, (const T*)k_pages, (const T*)v_pages, page_table, max_pages,
                                                        tok_slot, tok_pos, (const T*)gate, gate_stride, (T*)out, part_o, part_ml,
-                                                       nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale);
-  int rc = launch_status();
-  if (rc || n_splits == 1) return rc;
-  diff_attn_reduce_kernel<T><<<(unsigned)((size_t)n_rows * nKV * G), THREADS, sizeof(float) * MAPS * n_splits, st>>>(
-      part_o, part_ml, tok_slot, (const T*)gate, gate_stride, (T*)out, nKV * G, n_splits, lambda, sub_eps, out_scale);
+                                                       tickets, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale);
   return launch_status();
 }
 }  // namespace
@@ -330,10 +334,11 @@ DRYFT_API int dryft_diff_attn_rows_page() { return PAGE; }
 
 DRYFT_API int dryft_diff_attn_rows(int is_bf16, const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                                    int max_pages, const int* tok_slot, const int* tok_pos, const void* gate, int gate_stride,
-                                   void* out, float* part_o, float* part_ml, int n_rows, int nKV, int n_splits, float scale,
-                                   int window, int chunk, float lambda, float sub_eps, float out_scale, cudaStream_t st) {
+                                   void* out, float* part_o, float* part_ml, int* tickets, int n_rows, int nKV, int n_splits,
+                                   float scale, int window, int chunk, float lambda, float sub_eps, float out_scale, cudaStream_t st) {
   return is_bf16 ? launch<__nv_bfloat16>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, gate, gate_stride, out,
-                                         part_o, part_ml, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale, st)
+                                         part_o, part_ml, tickets, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps,
+                                         out_scale, st)
                  : launch<float>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, gate, gate_stride, out, part_o,
-                                 part_ml, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale, st);
+                                 part_ml, tickets, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale, st);
 }

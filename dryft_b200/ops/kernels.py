@@ -118,8 +118,8 @@ def diff_attention_rows_lib(qk_dim: int, v_dim: int, group: int, page: int) -> c
             path = build.build_library("diff_attn_rows", ("diff_attn_rows.cu",),
                                        {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
             lib = _load(path)
-            lib.dryft_diff_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _f, _i, _i, _f, _f,
-                                                 _f, _p]
+            lib.dryft_diff_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _f, _i, _i, _f,
+                                                 _f, _f, _p]
             lib.dryft_diff_attn_rows.restype = _i
             if (lib.dryft_diff_attn_rows_qk_dim(), lib.dryft_diff_attn_rows_v_dim(), lib.dryft_diff_attn_rows_group(),
                     lib.dryft_diff_attn_rows_page()) != (qk_dim, v_dim, group, page):
@@ -729,11 +729,12 @@ def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scal
         _need(part_ml, "part_ml", torch.float32)
         if part_o.numel() < n * n_heads * 2 * n_splits * v_dim or part_ml.numel() < n * n_heads * 2 * n_splits * 2:
             raise KernelError("diff_attn_rows: partial buffers too small for the split count")
+    tk = tickets(q.device, n * n_kv) if n_splits > 1 else None   # zeroed counters; every launch leaves them zero
     lib = diff_attention_rows_lib(kw // 2, v_dim, n_heads // n_kv, page)
     _ok(lib.dryft_diff_attn_rows(is_bf16, _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(tok_slot),
-                                 _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, n_splits,
-                                 float(scale), int(window or 0), int(chunk or 0), float(lam), float(sub_eps), float(out_scale),
-                                 _stream()), f"diff_attn_rows (dims {kw // 2}, {v_dim})", n_kernels=2 if n_splits > 1 else 1)
+                                 _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tk), n, n_kv,
+                                 n_splits, float(scale), int(window or 0), int(chunk or 0), float(lam), float(sub_eps),
+                                 float(out_scale), _stream()), f"diff_attn_rows (dims {kw // 2}, {v_dim})")
 
 
 # ----------------------------------------------------------------------------- mixture of experts

@@ -120,14 +120,16 @@ class DiffAttention:
         return None
 
     def _n_splits(self, n_rows: int, max_kv: int) -> int:
-        """Split a row's visible keys over blocks until the device is filled, a page per block at least."""
+        """Split a row's visible keys over blocks until the device is filled, two pages per block at least and at most 16
+        splits (the block that finishes last combines them: measured, more and shorter splits lengthen that tail by more
+        than they shorten the walk)."""
         span = max(1, max_kv)
         for bound in (self.window, self.chunk):
             if bound:
                 span = min(span, bound)
         pages = (span + self.rt.page_size - 1) // self.rt.page_size + (1 if (self.window or self.chunk) else 0)
         want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
-        return max(1, min(32, want, pages))
+        return max(1, min(16, want, (pages + 1) // 2))
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
         if owns_cache != self.own_kv:

@@ -32,7 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                    help="most tokens live requests hold at any time (padding not counted)")
     args = ap.parse_args(argv)
 
     import numpy as np
@@ -43,8 +43,11 @@ def main(argv=None) -> int:
 
     page = EngineOptions().page_size   # requests are counted in the cache's own unit
     n_tokens = max(page, (args.max_tokens + page - 1) // page * page)
-    opts = EngineOptions(dtype=args.dtype, max_batch=min(n_tokens // page, 4096), max_seq_len=n_tokens,
-                         max_tokens=n_tokens, page_size=page, cuda_graphs=False)
+    # --max-tokens counts tokens, the cache counts pages: every live request may leave most of its last page empty, so
+    # there is one page more per request that can be live at once (at least 64 of them, however few tokens they hold)
+    max_live = min(max(n_tokens // page, 64), 4096)
+    opts = EngineOptions(dtype=args.dtype, max_batch=max_live, max_seq_len=n_tokens,
+                         max_tokens=n_tokens + page * max_live, page_size=page, cuda_graphs=False)
     engine = Engine(args.model, opts)
     os.makedirs(args.out, exist_ok=True)
     slot_of = {}

@@ -45,6 +45,11 @@ CONFIGS: Dict[str, dict] = {
                  layer(heads=8, kv_heads=2, dim=16, vdim=16, chunk=7, diff=0.55),
                  layer(heads=8, kv_heads=2, dim=16, vdim=16, chunk=150, kv_from=1, diff=0.1, experts=16, groups=8, keep=5, top=5)],
                 width=64, vocab=130),
+    # every size a multiple of 16: the tensor-core prompt attention and the grouped expert products run here
+    "d": config([layer(heads=8, kv_heads=2, dim=16, vdim=32, chunk=80, ff=48, experts=16, groups=4, keep=3, top=4),
+                 layer(heads=8, kv_heads=2, dim=16, vdim=32, chunk=80, kv_from=0, ff=32, experts=8, groups=2, keep=2, top=2),
+                 layer(heads=4, kv_heads=1, dim=32, vdim=16, chunk=128, ff=64, experts=4, groups=1, keep=1, top=3)],
+                width=96, vocab=211, emb_scale=0.9),
 }
 
 
