@@ -17,7 +17,9 @@
 // Grid (rows, kv heads, splits).  One block serves the GROUP query heads of a kv head (2*GROUP maps) for one row over
 // a contiguous range of pages.  With one split the block finishes the row itself; otherwise every block leaves its
 // un-normalised partials (acc, m, l) per map and draws a ticket, and the block that draws the last ticket of its
-// (row, kv head) combines the splits and applies the epilogue -- one launch either way.
+// (row, kv head) combines the splits and applies the epilogue -- one launch either way.  In a step whose rows are each
+// their sequence's one new token (decode) the same launch also takes the per-map q/k norm and the cache write of the new
+// key and value (`fuse`), which prompts leave to kv_maps.cu.
 // No block waits on another block; there is no spin anywhere in this file.
 #include "common.cuh"
 #include <math.h>
@@ -66,6 +68,11 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
     T* __restrict__ out,                                            // [N, nH * DV]
     float* __restrict__ part_o, float* __restrict__ part_ml,        // [N, nH, 2, S, DV], [N, nH, 2, S, 2]
     int* __restrict__ tickets,                                      // [N * nKV] zeros; left zero
+    // fuse > 0 (a step in which every row is its sequence's one new token): the queries are normalised here from the
+    // projection row [q | k | v | ..] instead of being read from q; fuse == 2: the row's new key and value are normalised,
+    // written into the cache and used, by the block whose pages hold the row's own position
+    const T* __restrict__ proj, int proj_stride, const float* __restrict__ q_w, const float* __restrict__ k_w, float qk_eps,
+    int fuse, T* __restrict__ k_pages_w, T* __restrict__ v_pages_w,
     int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale) {
   using L = Smem<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -101,8 +108,26 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
   const int pg_begin = first_page + split * per_split;
   const int pg_end = min(pg_begin + per_split, last_page + 1);
 
-  // the block's GM query vectors: head g's map m is row g*MAPS + m, contiguous in q
-  for (int i = tid; i < GM * DQ; i += THREADS) qs[i] = to_f32<T>(q[((size_t)n * nH + (size_t)kvh * G) * KW + i]);
+  // the block's GM query vectors: head g's map m is row g*MAPS + m, contiguous in q (and in the projection row)
+  if (fuse) {
+    const T* prow = proj + (size_t)n * proj_stride;
+    for (int gm = warp; gm < GM; gm += NWARP) {   // y = T(w * x / sqrt(mean(x^2) + eps)), as the separate kernel rounds it
+      const T* src = prow + ((size_t)kvh * GM + gm) * DQ;
+      float ss = 0.f;
+      for (int c = lane; c < DQ; c += 32) {
+        const float x = to_f32<T>(src[c]);
+        ss = fmaf(x, x, ss);
+      }
+      ss = warp_sum(ss);
+      const float inv = 1.f / sqrtf(ss / (float)DQ + qk_eps);
+      for (int c = lane; c < DQ; c += 32) {
+        const float x = to_f32<T>(src[c]) * inv;
+        qs[gm * DQ + c] = rnd<T>(q_w ? x * q_w[c] : x);
+      }
+    }
+  } else {
+    for (int i = tid; i < GM * DQ; i += THREADS) qs[i] = to_f32<T>(q[((size_t)n * nH + (size_t)kvh * G) * KW + i]);
+  }
   if (tid < GM) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; a_s[tid] = 1.f; }
   float acc[DIMS_PER_THREAD][GM];
 #pragma unroll
@@ -139,6 +164,35 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
       *reinterpret_cast<CK*>(vt + r * DV + c * VEC) = v;
     }
     __syncthreads();
+    if (fuse == 2 && pg == last_page) {   // the row's own key and value: into the cache and into this tile
+      const T* prow = proj + (size_t)n * proj_stride + (size_t)nH * KW;   // behind the queries: k (nKV x KW), then v (nKV x DV)
+      const int r = pos - p0;
+      T* kdst = k_pages_w + (((size_t)page * nKV + kvh) * PAGE + r) * KW;
+      T* vdst = v_pages_w + (((size_t)page * nKV + kvh) * PAGE + r) * DV;
+      for (int m = warp; m < MAPS; m += NWARP) {
+        const T* src = prow + (size_t)kvh * KW + m * DQ;
+        float ss = 0.f;
+        for (int c = lane; c < DQ; c += 32) {
+          const float x = to_f32<T>(src[c]);
+          ss = fmaf(x, x, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)DQ + qk_eps);
+        for (int c = lane; c < DQ; c += 32) {
+          const float x = to_f32<T>(src[c]) * inv;
+          const T y = from_f32<T>(k_w ? x * k_w[c] : x);
+          kt[r * L::KSTRIDE + m * DQ + c] = y;
+          kdst[m * DQ + c] = y;
+        }
+      }
+      const T* vsrc = prow + (size_t)nKV * KW + (size_t)kvh * DV;
+      for (int c = tid; c < DV; c += THREADS) {
+        const T y = vsrc[c];
+        vt[r * DV + c] = y;
+        vdst[c] = y;
+      }
+      __syncthreads();
+    }
     // scores: item -> (map gm, key r); consecutive threads take consecutive keys
     for (int item = tid; item < GM * PAGE; item += THREADS) {
       const int gm = item / PAGE, r = item % PAGE;
@@ -299,11 +353,12 @@ __global__ void __launch_bounds__(THREADS) diff_attn_rows_kernel(
 template <typename T>
 int launch(const void* q, const void* k_pages, const void* v_pages, const int* page_table, int max_pages,
            const int* tok_slot, const int* tok_pos, const void* gate, int gate_stride, void* out, float* part_o, float* part_ml,
-           int* tickets, int n_rows, int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale,
+           int* tickets, const void* proj, int proj_stride, const float* q_w, const float* k_w, float qk_eps, int fuse, int n_rows, int nKV, int n_splits, float scale, int window, int chunk, float lambda, float sub_eps, float out_scale,
            cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 4096) return DRYFT_ERR_UNSUPPORTED;
   if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
+  if (fuse < 0 || fuse > 2 || (fuse && !proj) || (!fuse && !q)) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = Smem<T>::bytes() + sizeof(float) * (size_t)GM * n_splits;
   if (smem > 224 * 1024) return DRYFT_ERR_UNSUPPORTED;   // the kernel's few static bytes count against the same 227 KB
   static bool attr_set[64] = {false};   // per instantiation and device; set by the first (eager) launch
@@ -322,7 +377,8 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
   dim3 grid(n_rows, nKV, n_splits);
   diff_attn_rows_kernel<T><<<grid, THREADS, smem, st>>>((const T*)q, (const T*)k_pages, (const T*)v_pages, page_table, max_pages,
                                                        tok_slot, tok_pos, (const T*)gate, gate_stride, (T*)out, part_o, part_ml,
-                                                       tickets, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale);
+                                                       tickets, (const T*)proj, proj_stride, q_w, k_w, qk_eps, fuse, (T*)k_pages,
+                                                       (T*)v_pages, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale);
   return launch_status();
 }
 }  // namespace
@@ -334,11 +390,13 @@ DRYFT_API int dryft_diff_attn_rows_page() { return PAGE; }
 
 DRYFT_API int dryft_diff_attn_rows(int is_bf16, const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                                    int max_pages, const int* tok_slot, const int* tok_pos, const void* gate, int gate_stride,
-                                   void* out, float* part_o, float* part_ml, int* tickets, int n_rows, int nKV, int n_splits,
+                                   void* out, float* part_o, float* part_ml, int* tickets, const void* proj, int proj_stride,
+                                   const float* q_w, const float* k_w, float qk_eps, int fuse, int n_rows, int nKV, int n_splits,
                                    float scale, int window, int chunk, float lambda, float sub_eps, float out_scale, cudaStream_t st) {
   return is_bf16 ? launch<__nv_bfloat16>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, gate, gate_stride, out,
-                                         part_o, part_ml, tickets, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps,
-                                         out_scale, st)
+                                         part_o, part_ml, tickets, proj, proj_stride, q_w, k_w, qk_eps, fuse, n_rows, nKV, n_splits,
+                                         scale, window, chunk, lambda, sub_eps, out_scale, st)
                  : launch<float>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, gate, gate_stride, out, part_o,
-                                 part_ml, tickets, n_rows, nKV, n_splits, scale, window, chunk, lambda, sub_eps, out_scale, st);
+                                 part_ml, tickets, proj, proj_stride, q_w, k_w, qk_eps, fuse, n_rows, nKV, n_splits, scale, window,
+                                 chunk, lambda, sub_eps, out_scale, st);
 }

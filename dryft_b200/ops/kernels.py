@@ -118,8 +118,8 @@ def diff_attention_rows_lib(qk_dim: int, v_dim: int, group: int, page: int) -> c
             path = build.build_library("diff_attn_rows", ("diff_attn_rows.cu",),
                                        {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
             lib = _load(path)
-            lib.dryft_diff_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _f, _i, _i, _f,
-                                                 _f, _f, _p]
+            lib.dryft_diff_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _p, _p, _f, _i, _i, _i,
+                                                 _i, _f, _i, _i, _f, _f, _f, _p]
             lib.dryft_diff_attn_rows.restype = _i
             if (lib.dryft_diff_attn_rows_qk_dim(), lib.dryft_diff_attn_rows_v_dim(), lib.dryft_diff_attn_rows_group(),
                     lib.dryft_diff_attn_rows_page()) != (qk_dim, v_dim, group, page):
@@ -701,26 +701,46 @@ def kv_maps_store(proj, q_norm_w, k_norm_w, tok_slot, tok_pos, q_out, k_pages, v
 
 def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: float, lam: float, sub_eps: float,
                    out_scale: float, window: Optional[int] = None, chunk: Optional[int] = None, gate=None, gate_col: int = 0,
-                   n_splits: int = 1, part_o=None, part_ml=None) -> None:
+                   n_splits: int = 1, part_o=None, part_ml=None, proj=None, n_heads: int = 0, q_norm_w=None, k_norm_w=None,
+                   qk_eps: float = 0.0, write_kv: bool = False) -> None:
     """Differential attention of independent rows: ``q [n, heads, 2*dim]`` (normalised), keys ``[pages, kv, page, 2*dim]``,
     values ``[pages, kv, page, v_dim]``; ``out [n, heads*v_dim] = gate * out_scale * unit_rms(a1 - lam * a2)``.  ``gate``: a
-    2-D tensor whose columns ``gate_col .. gate_col + heads - 1`` hold one logit per head (sigmoid is applied)."""
-    n, n_heads, kw = q.shape
-    is_bf16 = _act(q, "q")
-    _need(q, "q")
+    2-D tensor whose columns ``gate_col .. gate_col + heads - 1`` hold one logit per head (sigmoid is applied).
+
+    With ``proj`` instead of ``q`` (a step whose rows are each their sequence's one new token): rows of ``proj`` are
+    ``[q | k | v | ...]`` as ``kv_maps_store`` takes them, the per-map norm of the ``n_heads`` queries happens inside, and
+    with ``write_kv`` so do the norm and the cache write of each row's new key and value -- one launch for all of it."""
+    if proj is not None:
+        if q is not None or n_heads <= 0:
+            raise KernelError("diff_attn_rows: give either q or (proj, n_heads)")
+        n, kw = proj.shape[0], k_pages.shape[3]
+        _need(proj, "proj", k_pages.dtype)
+        is_bf16 = _act(proj, "proj")
+        need_w = n_heads * kw + ((k_pages.shape[1] * kw + k_pages.shape[1] * v_pages.shape[3]) if write_kv else 0)
+        if proj.dim() != 2 or proj.shape[1] < need_w:
+            raise KernelError(f"diff_attn_rows: projection rows have {tuple(proj.shape)}, need at least {need_w} columns")
+        for w_, nm in ((q_norm_w, "q norm weight"), (k_norm_w, "k norm weight")):
+            if w_ is not None:
+                _need(w_, nm, torch.float32, (kw // 2,))
+        q_dtype = proj.dtype
+    else:
+        n, n_heads, kw = q.shape
+        is_bf16 = _act(q, "q")
+        _need(q, "q")
+        q_dtype = q.dtype
     n_kv, page, v_dim = k_pages.shape[1], k_pages.shape[2], v_pages.shape[3]
-    _need(k_pages, "k_pages", q.dtype, (None, n_kv, page, kw))
-    _need(v_pages, "v_pages", q.dtype, (k_pages.shape[0], n_kv, page, v_dim))
+    _need(k_pages, "k_pages", q_dtype, (None, n_kv, page, kw))
+    _need(v_pages, "v_pages", q_dtype, (k_pages.shape[0], n_kv, page, v_dim))
     for t, nm in ((page_table, "page_table"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
         _need(t, nm, torch.int32)
     if tok_slot.numel() < n or tok_pos.numel() < n:
         raise KernelError("diff_attn_rows: token index arrays shorter than the batch")
-    _need(out, "attention output", q.dtype, (n, n_heads * v_dim))
+    _need(out, "attention output", q_dtype, (n, n_heads * v_dim))
     if n_heads % n_kv or kw % 2:
         raise KernelError(f"diff_attn_rows: {n_heads} query heads / {n_kv} kv heads / key rows of {kw}")
     gate_ptr, gate_stride = None, 0
     if gate is not None:
-        _need(gate, "gate", q.dtype)
+        _need(gate, "gate", q_dtype)
         if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
             raise KernelError("diff_attn_rows: gate columns outside the gate tensor")
         gate_ptr, gate_stride = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
@@ -729,10 +749,12 @@ def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scal
         _need(part_ml, "part_ml", torch.float32)
         if part_o.numel() < n * n_heads * 2 * n_splits * v_dim or part_ml.numel() < n * n_heads * 2 * n_splits * 2:
             raise KernelError("diff_attn_rows: partial buffers too small for the split count")
-    tk = tickets(q.device, n * n_kv) if n_splits > 1 else None   # zeroed counters; every launch leaves them zero
+    tk = tickets(out.device, n * n_kv) if n_splits > 1 else None   # zeroed counters; every launch leaves them zero
+    fuse = 0 if proj is None else (2 if write_kv else 1)
     lib = diff_attention_rows_lib(kw // 2, v_dim, n_heads // n_kv, page)
     _ok(lib.dryft_diff_attn_rows(is_bf16, _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(tok_slot),
-                                 _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tk), n, n_kv,
+                                 _ptr(tok_pos), gate_ptr, gate_stride, _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tk), _ptr(proj),
+                                 proj.shape[1] if proj is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(qk_eps), fuse, n, n_kv,
                                  n_splits, float(scale), int(window or 0), int(chunk or 0), float(lam), float(sub_eps),
                                  float(out_scale), _stream()), f"diff_attn_rows (dims {kw // 2}, {v_dim})")
 

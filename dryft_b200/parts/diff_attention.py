@@ -138,11 +138,23 @@ class DiffAttention:
         n = h.shape[0]
         dev = h.device
         proj = linear(h, self.w_in, self.rt)
+        o = torch.empty((n, self.o_cols), dtype=h.dtype, device=dev)
+        gate = proj if self.has_gate else None
+        if ctx.decode:
+            # every row is its sequence's one new token: per-map norms, the cache write and attention in one launch
+            s = self._n_splits(n, ctx.max_kv)
+            part_o = part_ml = None
+            if s > 1:
+                part_o = torch.empty((n, self.n_heads, self.MAPS, s, self.v_dim), dtype=torch.float32, device=dev)
+                part_ml = torch.empty((n, self.n_heads, self.MAPS, s, 2), dtype=torch.float32, device=dev)
+            K.diff_attn_rows(None, cache.k, cache.v, cache.page_table, ctx.tok_slot, ctx.tok_pos, o, self.scale, self.lam, self.eps,
+                             self.out_scale, window=self.window, chunk=self.chunk, gate=gate, gate_col=self.gate_col, n_splits=s,
+                             part_o=part_o, part_ml=part_ml, proj=proj, n_heads=self.n_heads, q_norm_w=self.q_norm_w,
+                             k_norm_w=self.k_norm_w, qk_eps=self.eps, write_kv=self.own_kv)
+            return linear(o, self.w_o, self.rt)
         q = torch.empty((n, self.n_heads, self.MAPS * self.qk_dim), dtype=h.dtype, device=dev)
         K.kv_maps_store(proj, self.q_norm_w, self.k_norm_w, ctx.tok_slot, ctx.tok_pos, q, cache.k, cache.v, cache.page_table,
                         self.n_heads, self.n_kv, self.MAPS, self.qk_dim, self.v_dim, self.eps, write_kv=self.own_kv)
-        o = torch.empty((n, self.o_cols), dtype=h.dtype, device=dev)
-        gate = proj if self.has_gate else None
         if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0 and ctx.tile_size <= PREFILL_TILE:
             K.diff_attn_prefill(q, cache.k, cache.v, cache.page_table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos, o,
                                 ctx.n_tiles, self.scale, self.lam, self.eps, self.out_scale, window=self.window, chunk=self.chunk,

@@ -117,8 +117,9 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
 
 FP32_TOL = 3e-5     # sums in another order, device sin / exp
 BF16_TOL = 0.05     # what rounding at every stage does to logits of these models, with room
-BF16_MOST = 0.9     # share of rows that must be within BF16_TOL: bfloat16 noise can flip a router's close call,
-                    # which moves that token's logits by far more than rounding does (the 32-bit path is the sharp test)
+BF16_MOST = 0.9     # share of rows that must be within BF16_TOL (one row may always be off when there are two or more):
+                    # bfloat16 noise can flip a router's close call, which moves that token's logits by far more than
+                    # rounding does (the 32-bit path is the sharp test)
 
 
 def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str) -> None:
@@ -127,6 +128,7 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str) -
     if dtype == "float32":
         assert float(e.max()) <= FP32_TOL, f"{what}: row {int(e.argmax())} off by {float(e.max()):.3g}"
     else:
-        share = float((e <= BF16_TOL).double().mean())
-        assert share >= BF16_MOST and float(e.median()) <= BF16_TOL / 2, \
-            f"{what}: {share:.2f} of the rows within {BF16_TOL}, median {float(e.median()):.3g}"
+        over = int((e > BF16_TOL).sum())
+        allowed = 0 if e.numel() < 2 else max(1, int((1.0 - BF16_MOST) * e.numel()))
+        assert over <= allowed and float(e.median()) <= BF16_TOL / 2, \
+            f"{what}: {over} of {e.numel()} rows off by more than {BF16_TOL} ({allowed} allowed), median {float(e.median()):.3g}"
