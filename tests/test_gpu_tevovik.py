@@ -51,11 +51,13 @@ def test_whole_prompts_decoding_portions_and_batches(tmp_path_factory, name, dty
     reqs = M.prompts(cfg, lengths, seed=3)
     with torch.inference_mode():
         # whole prompts, logits at every place (the first tokens included)
+        pairs = []
         for toks in reqs:
             s = eng.cache.open_sequences(1)
             got = eng.stepper.step(s, [toks], [list(range(len(toks)))])
             eng.cache.close_sequences(s)
-            M.assert_close(got, plain_logits(entry, toks), dtype, f"{name} whole prompt of {len(toks)}")
+            pairs.append((got, plain_logits(entry, toks), f"prompt of {len(toks)}"))
+        M.assert_all_close(pairs, dtype, f"{name} whole prompts")
         # most of the prompt at once, the rest token by token (across chunk and page edges)
         for toks in reqs[3:]:
             head = max(1, len(toks) - 70)
@@ -80,10 +82,11 @@ def test_whole_prompts_decoding_portions_and_batches(tmp_path_factory, name, dty
         heads = [max(1, len(t) - 12) for t in batch]
         slots = eng.cache.open_sequences(len(batch))
         got = eng.stepper.step(slots, [t[:h] for t, h in zip(batch, heads)], [list(range(h)) for h in heads])
-        at = 0
+        at, pairs = 0, []
         for t, h in zip(batch, heads):
-            M.assert_close(got[at:at + h], plain_logits(entry, t)[:h], dtype, f"{name} batched prompt of {h}")
+            pairs.append((got[at:at + h], plain_logits(entry, t)[:h], f"prompt of {h}"))
             at += h
+        M.assert_all_close(pairs, dtype, f"{name} batched prompts")
         live = list(range(len(batch)))
         step = 0
         collected = {b: [] for b in live}
@@ -95,8 +98,8 @@ def test_whole_prompts_decoding_portions_and_batches(tmp_path_factory, name, dty
             done = [b for b in live if heads[b] + step >= len(batch[b])]
             eng.cache.close_sequences([slots[b] for b in done])
             live = [b for b in live if b not in done]
-        for b, rows in collected.items():
-            M.assert_close(torch.cat(rows), plain_logits(entry, batch[b])[heads[b]:], dtype, f"{name} batched decoding of request {b}")
+        M.assert_all_close([(torch.cat(rows), plain_logits(entry, batch[b])[heads[b]:], f"request {b}") for b, rows in collected.items()],
+                           dtype, f"{name} batched decoding")
     eng.cache.check()
 
 

@@ -132,3 +132,13 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str) -
         allowed = 0 if e.numel() < 2 else max(1, int((1.0 - BF16_MOST) * e.numel()))
         assert over <= allowed and float(e.median()) <= BF16_TOL / 2, \
             f"{what}: {over} of {e.numel()} rows off by more than {BF16_TOL} ({allowed} allowed), median {float(e.median()):.3g}"
+
+
+def assert_all_close(pairs, dtype: str, what: str) -> None:
+    """``pairs``: (got, want, label).  In 32-bit every pair is held to the sharp tolerance on its own; in bfloat16 the rows
+    of all pairs are judged together (a single row, a one-token request say, cannot be judged statistically)."""
+    if dtype == "float32":
+        for got, want, label in pairs:
+            assert_close(got, want, dtype, f"{what}: {label}")
+    else:
+        assert_close(torch.cat([g.detach().float().cpu() for g, _, _ in pairs]), torch.cat([w for _, w, _ in pairs]), dtype, what)
