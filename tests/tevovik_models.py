@@ -50,6 +50,13 @@ CONFIGS: Dict[str, dict] = {
                  layer(heads=8, kv_heads=2, dim=16, vdim=32, chunk=80, kv_from=0, ff=32, experts=8, groups=2, keep=2, top=2),
                  layer(heads=4, kv_heads=1, dim=32, vdim=16, chunk=128, ff=64, experts=4, groups=1, keep=1, top=3)],
                 width=96, vocab=211, emb_scale=0.9),
+    # a width of 256 (the decode products compiled per inner size), and every expert chosen: no router's close call can
+    # move a logit here, so bfloat16 is compared as sharply as rounding allows
+    "e": config([layer(heads=8, kv_heads=2, dim=32, vdim=48, chunk=128, ff=128, experts=4, groups=1, keep=1, top=4),
+                 layer(heads=8, kv_heads=2, dim=32, vdim=48, chunk=128, kv_from=0, ff=128, experts=4, groups=2, keep=2, top=4),
+                 layer(heads=4, kv_heads=4, dim=64, vdim=64, chunk=50, mlp=False),
+                 layer(heads=4, kv_heads=4, dim=64, vdim=64, chunk=200, kv_from=2, ff=256, experts=2, groups=1, keep=1, top=2)],
+                width=256, vocab=1000),
 }
 
 
