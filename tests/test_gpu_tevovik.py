@@ -213,3 +213,26 @@ def test_trace_replay_as_a_child_process(tmp_path_factory, tmp_path, dtype):
     M.assert_close(got1, torch.cat([plain_logits(entry, t)[-1:] for t in reqs]), dtype, "replayed decode step")
     got3 = torch.from_numpy(np.fromfile(os.path.join(out, "3.f32"), dtype="<f4").reshape(-1, cfg["vocab"]).copy())
     M.assert_close(got3, plain_logits(entry, reqs[1] + [5])[-1:], dtype, "a request id used again")
+
+
+def test_command_line_generates_and_samples(tmp_path_factory):
+    """``python -m dryft_b200 generate`` on a Tevovik model folder: greedy tokens are the plain ones, sampling is seeded."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import helpers as H
+
+    entry = model("a", tmp_path_factory)
+    cfg, tensors = entry[0], entry[1]
+    base = [sys.executable, "-m", "dryft_b200", "generate", "--model", entry[2], "--dtype", "float32", "--max-batch", "4",
+            "--max-seq-len", "128", "--prompt-ids", "5,17,3,60,9", "--prompt-ids", "7,7,7", "--max-new-tokens", "6"]
+    run = lambda extra: subprocess.run(base + extra, capture_output=True, text=True, timeout=600, cwd=H.ROOT)
+    greedy = run([])
+    assert greedy.returncode == 0, greedy.stderr[-2000:]
+    rows = [json.loads(ln) for ln in greedy.stdout.splitlines() if ln.startswith("{")]
+    assert [r["tokens"] for r in rows] == [P.greedy(cfg, tensors, p, 6) for p in ([5, 17, 3, 60, 9], [7, 7, 7])]
+    a, b, c = run(["--temperature", "0.9", "--top-k", "7", "--seed", "3"]), run(["--temperature", "0.9", "--top-k", "7", "--seed", "3"]), \
+        run(["--temperature", "0.9", "--top-k", "7", "--seed", "4"])
+    assert a.returncode == 0 and a.stdout == b.stdout and a.stdout != c.stdout
