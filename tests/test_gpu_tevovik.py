@@ -42,7 +42,7 @@ def engine(entry, dtype, **kw):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e", "f"])
 def test_whole_prompts_decoding_portions_and_batches(tmp_path_factory, name, dtype):
     entry = model(name, tmp_path_factory)
     cfg = entry[0]

@@ -23,7 +23,7 @@ def test_registry_picks_the_design_by_its_architecture_string():
     assert isinstance(config_from_dict(preset("tevovik-tiny")), TevovikConfig)
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e", "f"])
 def test_config_round_trip_and_spec(name):
     raw = M.CONFIGS[name]
     cfg = TevovikConfig.from_dict(raw)

@@ -57,6 +57,12 @@ CONFIGS: Dict[str, dict] = {
                  layer(heads=4, kv_heads=4, dim=64, vdim=64, chunk=50, mlp=False),
                  layer(heads=4, kv_heads=4, dim=64, vdim=64, chunk=200, kv_from=2, ff=256, experts=2, groups=1, keep=1, top=2)],
                 width=256, vocab=1000),
+    # sizes that fit no vector, tile or tensor-core step (odd map and value sizes, three query heads on one kv head, a width
+    # of 100): every kernel's element-by-element form and the library's products at unaligned sizes
+    "f": config([layer(heads=3, kv_heads=1, dim=24, vdim=20, chunk=10, ff=36, experts=5, groups=1, keep=1, top=5),
+                 layer(heads=3, kv_heads=1, dim=5, vdim=7, chunk=70, ff=9, experts=5, groups=5, keep=5, top=5),
+                 layer(heads=5, kv_heads=5, dim=6, vdim=10, chunk=None, ff=18, experts=3, groups=1, keep=1, top=3)],
+                width=100, vocab=99),
 }
 
 
