@@ -236,3 +236,30 @@ def test_command_line_generates_and_samples(tmp_path_factory):
     a, b, c = run(["--temperature", "0.9", "--top-k", "7", "--seed", "3"]), run(["--temperature", "0.9", "--top-k", "7", "--seed", "3"]), \
         run(["--temperature", "0.9", "--top-k", "7", "--seed", "4"])
     assert a.returncode == 0 and a.stdout == b.stdout and a.stdout != c.stdout
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_forty_unequal_requests_at_once(tmp_path_factory, dtype):
+    """More rows than the few-row kernels take: the decode steps go through the library's products, the router's two-launch
+    form and, from 32 rows on, the grouped expert products; requests end one after another."""
+    entry = model("d", tmp_path_factory)
+    cfg = entry[0]
+    eng = engine(entry, dtype, max_batch=64, max_seq_len=256, max_tokens=8192)
+    reqs = M.prompts(cfg, [3 + (7 * i) % 50 for i in range(40)], seed=4)
+    with torch.inference_mode():
+        slots = eng.cache.open_sequences(len(reqs))
+        heads = [max(1, len(r) - 5) for r in reqs]
+        got = eng.stepper.step(slots, [r[:h] for r, h in zip(reqs, heads)], [[h - 1] for h in heads])
+        pairs = [(got[i:i + 1], plain_logits(entry, reqs[i])[heads[i] - 1:heads[i]], f"prompt {i}") for i in range(len(reqs))]
+        live, step, rows = list(range(len(reqs))), 0, {b: [] for b in range(len(reqs))}
+        while live:
+            got = eng.stepper.step([slots[b] for b in live], [[reqs[b][heads[b] + step]] for b in live], [[0]] * len(live))
+            for i, b in enumerate(live):
+                rows[b].append(got[i:i + 1])
+            step += 1
+            done = [b for b in live if heads[b] + step >= len(reqs[b])]
+            eng.cache.close_sequences([slots[b] for b in done])
+            live = [b for b in live if b not in done]
+        pairs += [(torch.cat(r), plain_logits(entry, reqs[b])[heads[b]:], f"request {b}") for b, r in rows.items() if r]
+    M.assert_all_close(pairs, dtype, "forty requests")
+    eng.cache.check()
