@@ -33,7 +33,7 @@ class KVNeed:
     """What an attention-like mixer asks of the cache: keys and values of this shape, all of
     them (``window=None``) or the last ``window``.  ``v_head_dim``: the size of a value row where it differs from
     a key row's ``head_dim`` (a key row may hold several score maps' keys).  ``chunk``: queries only see keys of
-    their own block of ``chunk`` positions (counted from position 0), so pages wholly before the block of the
+    their own block of ``chunk`` positions (blocks aligned to the sequence's start), so pages wholly before the block of the
     next position are given back."""
 
     kv_heads: int

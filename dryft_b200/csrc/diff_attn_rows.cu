@@ -10,8 +10,8 @@
 // (the gate is optional: one logit per token and head, read from a row of the projection output).
 // Row n at position p of slot s sees the keys j <= p with
 //     j >= p + 1 - window        (window > 0: the last `window` keys)
-//     j >= floor(p / chunk) * chunk   (chunk > 0: only keys of the query's own block of `chunk` positions,
-//                                      counted from position 0 of the sequence)
+//     j >= floor(p / chunk) * chunk   (chunk > 0: only keys of the query's own block of `chunk` positions; blocks are
+//                                      aligned to the sequence's start, whatever portions it was fed in)
 // Scores, maxima, sums, the combination and its norm are 32-bit.
 //
 // Grid (rows, kv heads, splits).  One block serves the GROUP query heads of a kv head (2*GROUP maps) for one row over

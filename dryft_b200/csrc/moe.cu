@@ -1,7 +1,8 @@
 // Mixture of experts: the router's choice and the experts evaluated assignment by assignment.
 //
-//   moe_route     scores s = softmax(logits) over all E experts (32-bit).  The experts form `n_groups` equal groups of
-//                 neighbours; a group scores its largest member; only experts of the `keep` best groups can be chosen
+//   moe_route     scores s = softmax(logits) over all E experts (32-bit).  Expert e belongs to group e / (E / n_groups)
+//                 (contiguous, equally sized); a group is ranked by the maximum score among its members, and selection
+//                 is restricted to the `keep` highest-ranked groups
 //                 (n_groups = keep = 1: no groups).  The `top` allowed experts with the largest scores are chosen;
 //                 their weights are the scores themselves, or the scores divided by their sum (`renorm`).
 //                 Ties go to the lower index.  One warp per token.  moe_route_rows is the same for few tokens with the

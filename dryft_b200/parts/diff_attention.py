@@ -9,8 +9,8 @@ value size and ``h`` the mixer's input:
   -> every (head, map) vector of q and k gets an RMS norm over ``d`` (one weight vector for all queries, one for
   all keys); no rotation -> k and v are written into the cache at the token's position (``csrc/kv_maps.cu``)
   -> per map, softmax attention with ``score = q . k * scale`` over the keys the query may see: ``j <= i``, inside
-  the last ``window`` keys if there is a window, and inside the query's own block of ``chunk`` positions (counted
-  from position 0 of the sequence) if there is a chunk size
+  the last ``window`` keys if there is a window, and inside the query's own block of ``chunk`` positions (blocks
+  ``[m chunk, (m+1) chunk)`` of the sequence's positions, however the prompt was fed) if there is a chunk size
   -> ``o = a1 - lambda * a2`` with ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff`` (one number per layer),
   ``o <- o / sqrt(mean(o^2) + eps) * (1 - diff)`` over the head's ``dv`` values, ``o <- o * sigmoid(g_head)``
   -> ``@ W_o.T``.

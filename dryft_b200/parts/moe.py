@@ -1,10 +1,10 @@
 """Mixture-of-experts feed-forward with group-limited top-k routing.
 
 ``E`` small SwiGLU experts (``down(silu(gate(h)) * up(h))``, no biases); a token uses ``top`` of them.  Router:
-``z = W_router h`` and ``s = softmax(z)`` over all experts in 32-bit; the experts form ``groups`` equal groups of
-neighbours, a group scores its largest member, and only experts of the ``keep`` best groups can be chosen; the ``top``
-largest scores among those are the token's experts, weighted by their scores ``s`` as they are (or divided by their sum
-with ``renormalize``).  The output is the weighted sum of the chosen experts' outputs.
+``z = W_router h`` and ``s = softmax(z)`` over all experts in 32-bit; expert ``e`` belongs to group ``e // (E / groups)`` (contiguous and equally
+sized), a group is ranked by the maximum of its members' scores, and selection is restricted to the ``keep`` highest-ranked
+groups; within them the ``top`` largest scores name the token's experts, each weighted by its own score ``s`` with no
+rescaling (or with the scores divided by their sum, ``renormalize``).  The output is the weighted sum of the chosen experts' outputs.
 
 The router's product leaves 32-bit logits (32-bit accumulation over the activations as the layer hands them over); the
 choice is ``csrc/moe.cu:moe_route``.  The experts run assignment by assignment for few tokens and in the 32-bit path

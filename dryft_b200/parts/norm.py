@@ -48,8 +48,8 @@ class RMSNorm:
 
 @register_norm("rmsnorm_offset")
 class OffsetRMSNorm:
-    """``x / sqrt(mean(x^2) + eps) * (offset + w)``, all of it in 32-bit and rounded once: the norm with a weight
-    stored around zero (``offset = 1``).  Its input may be a 32-bit stream while the output has the activation type.
+    """``x / sqrt(mean(x^2) + eps) * (offset + w)``, all of it in 32-bit and rounded once: the norm whose stored weight is a
+    deviation from one (``offset = 1``).  Its input may be a 32-bit stream while the output has the activation type.
     It does not offer ``rms_params`` (its arithmetic is not the one the decode products fold into themselves).
     ``add_into`` is the form a layer with the norm on the sublayer's *output* uses: ``x32 += norm(y)``.
     ``params["name"]`` is the weight's tensor name behind the prefix (default ``weight``)."""

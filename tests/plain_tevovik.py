@@ -100,8 +100,9 @@ def diff_attention(h: torch.Tensor, pos: torch.Tensor, t: Mapping[str, torch.Ten
 
 
 def route(h: torch.Tensor, w_router: torch.Tensor, r: Mapping):
-    """Chosen experts ``[T, R]`` and their weights: softmax over all experts, the best ``keep`` of ``count`` equal
-    groups of neighbours (a group scores its largest member), the ``R`` largest scores among those, unscaled."""
+    """Chosen experts ``[T, R]`` and their weights: ``s = softmax(z)`` over all ``E`` experts; group ``g`` holds experts
+    ``g * E/count .. (g+1) * E/count - 1`` and is ranked by ``max s`` inside it; among the ``keep`` highest-ranked groups the
+    ``R`` largest ``s`` are chosen and used as weights without rescaling."""
     E, R = r["experts"], r["top"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
     n_g, keep = groups["count"], groups["keep"]
