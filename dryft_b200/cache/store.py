@@ -34,13 +34,15 @@ class KVNeed:
     them (``window=None``) or the last ``window``.  ``v_head_dim``: the size of a value row where it differs from
     a key row's ``head_dim`` (a key row may hold several score maps' keys).  ``chunk``: queries only see keys of
     their own block of ``chunk`` positions (blocks aligned to the sequence's start), so pages wholly before the block of the
-    next position are given back."""
+    next position are given back.  ``values=False``: the mixer keeps one row per token only (a latent that both its keys
+    and its values are made from); no value pages exist and ``CacheEntry.v`` is None."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -58,7 +60,7 @@ class CacheEntry:
     """What one run step's mixer gets: its K and V pages and its group's page table."""
 
     k: torch.Tensor  # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]   # None for a group that keeps keys only
     page_table: torch.Tensor  # [max_slots, max_pages_per_slot] int32
     page_size: int
     window: Optional[int]
@@ -76,7 +78,7 @@ class _KVGroup:
                                  need.chunk if trim else None)
         shape = (len(run_steps), n_pages, need.kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device) if need.values else None
         self.page_table_host = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32)
         self.page_table = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32, device=device)
         self.dirty: set = set()
@@ -86,7 +88,7 @@ class _KVGroup:
         self.staged: Optional[torch.cuda.Event] = None
 
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (self.v.numel() if self.v is not None else 0)) * self.k.element_size()
 
 
 class SequenceCache:
@@ -107,6 +109,7 @@ class SequenceCache:
         page_size: int,
         dtype: torch.dtype,
         device: torch.device,
+        named_states: Optional[Mapping[str, StateNeed]] = None,
     ):
         if page_size <= 0 or page_size % 16:
             raise CacheError(f"page_size must be a positive multiple of 16, got {page_size}")
@@ -127,6 +130,10 @@ class SequenceCache:
         self._groups: List[_KVGroup] = []
         self._entry_of: Dict[int, Tuple[int, int]] = {}  # run step -> (group index, index in group)
         self._states: Dict[int, torch.Tensor] = {}
+        # per-sequence state of parts outside the layers (an embedding that remembers the token before), by name
+        self._named: Dict[str, torch.Tensor] = {
+            name: torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
+            for name, need in (named_states or {}).items()}
         by_need: Dict[KVNeed, List[int]] = {}
         for i, (kv, st) in enumerate(needs):
             if borrow[i] is not None:
@@ -163,14 +170,18 @@ class SequenceCache:
         if loc is None:
             return None
         g = self._groups[loc[0]]
-        return CacheEntry(g.k[loc[1]], g.v[loc[1]], g.page_table, self.page_size, g.need.window)
+        return CacheEntry(g.k[loc[1]], g.v[loc[1]] if g.v is not None else None, g.page_table, self.page_size, g.need.window)
 
     def state(self, run_step: int):
         """The run step's state ``[slots, *shape]`` (a mapping of such tensors if it asked with a mapping), or None."""
         return self._states.get(run_step)
 
+    def named_state(self, name: str) -> Optional[torch.Tensor]:
+        """The state ``[slots, *shape]`` asked for under ``name`` (zeroed when a slot is taken), or None."""
+        return self._named.get(name)
+
     def _state_tensors(self) -> List[torch.Tensor]:
-        seen: Dict[int, torch.Tensor] = {}
+        seen: Dict[int, torch.Tensor] = {id(t): t for t in self._named.values()}
         for st in self._states.values():
             for t in (st.values() if isinstance(st, dict) else (st,)):
                 seen[id(t)] = t

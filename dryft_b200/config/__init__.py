@@ -3,6 +3,7 @@
 from .spec import ExtraPart, LayerSpec, ModelSpec, PartSpec, RunStep
 from .qwen3 import ConfigError, Qwen3Config
 from .tevovik import TevovikConfig
+from .vobusun import VobusunConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -17,10 +18,11 @@ from .presets import PRESETS, preset
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict)
 register_architecture("Tevovik", TevovikConfig.from_dict)
+register_architecture("Vobusun", VobusunConfig.from_dict)
 
 __all__ = [
     "ExtraPart",
-    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "PRESETS", "Qwen3Config", "RunStep", "TevovikConfig",
+    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "PRESETS", "Qwen3Config", "RunStep", "TevovikConfig", "VobusunConfig",
     "architecture_of", "config_from_dict", "known_architectures", "load_config", "load_model_spec",
     "preset", "register_architecture", "unregister_architecture",
 ]

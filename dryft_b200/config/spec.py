@@ -33,8 +33,8 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class ExtraPart:
-    """A part of a layer beyond the usual four: ``family`` says which registry builds it ("norm", "ffn" or
-    "mixer"), ``name`` is what the block arrangement knows it by (a norm behind the mixer's output, say)."""
+    """A part of a layer beyond the usual four: ``family`` says which registry builds it ("norm", "ffn", "mixer" or
+    "connection"), ``name`` is what the block arrangement knows it by (a norm behind the mixer's output, say)."""
 
     name: str
     family: str
@@ -106,8 +106,8 @@ class ModelSpec:
             if len(set(names)) != len(names):
                 raise ValueError(f"layer {i}: two extra parts share a name: {names}")
             for e in layer.extra:
-                if e.family not in ("norm", "ffn", "mixer"):
-                    raise ValueError(f"layer {i}: extra part {e.name!r} has family {e.family!r}; known: norm, ffn, mixer")
+                if e.family not in ("norm", "ffn", "mixer", "connection"):
+                    raise ValueError(f"layer {i}: extra part {e.name!r} has family {e.family!r}; known: norm, ffn, mixer, connection")
         for i, st in enumerate(self.schedule):
             if not 0 <= st.layer < len(self.layers):
                 raise ValueError(f"run step {i} names layer {st.layer}, but there are {len(self.layers)} layers")

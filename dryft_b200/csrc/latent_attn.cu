@@ -1,0 +1,243 @@
+// Attention whose keys and values are low-rank latents: the cache holds, per token, one row
+//     [ c (kv_rank entries, normalised) | k_rot (rot_dim entries, rotated) ]
+// shared by all heads, and the per-head key and value matrices are folded into the query and the output:
+//     score(i, j) = ( (W_uk,h^T q_plain,i) . c_j + q_rot,i . k_rot,j ) * scale          o_lat,i = sum_j p(i, j) c_j
+// (the caller multiplies q_plain by W_uk,h^T before and o_lat by W_uv,h after, as matrix products).
+//
+// latent_prep        per token, from one projection row [.. dq (q_rank) .. dkv (kv_rank + rot_dim) ..]:
+//                      cq = T( rmsnorm(dq) * w_q )                        -> the query up-projection's input
+//                      c  = rmsnorm(dkv[:kv_rank]) * w_kv ; k_rot = rotate(dkv[kv_rank:]) at the token's position
+//                      cache row (slot, position) <- T([c | k_rot])
+// latent_attn_rows   one block per (query token, group of heads), a warp per head.  Keys position-window+1 .. position
+//                    (all keys from 0 if window is 0) are staged 32 at a time in shared memory as floats; a lane takes a
+//                    key for the scores (softmax running maximum and sum in 32-bit) and a slice of the latent for the
+//                    weighted sum.  The query's rotated part is rotated here.  Heads-major input and output:
+//                    q_lat [H, N, kv_rank] (32-bit), q [N, H, q_stride] with the rotated part at q_rot_off,
+//                    o_lat [H, N, kv_rank].
+// head_gate          out[n, h, :] = T( o[h, n, :] * sigmoid(gate_logit[n, h]) )
+//
+// Rotation: pairs (2i, 2i+1) when `interleaved`, else (i, i + R/2); angle = position * inv_freq[i] in 32-bit.
+// Norms, angles, scores, softmax and the weighted sum are 32-bit whatever the cache type T.  Sizes are runtime arguments
+// (kv_rank up to 512).  No block waits on another.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int PREP_THREADS = 256;
+constexpr int HPB = 4;         // heads (warps) per block of latent_attn_rows
+constexpr int KT = 32;         // keys per staged tile
+
+__device__ __forceinline__ float rotated(const float* v, int d, int R, bool interleaved, float pos, const float* inv_freq) {
+  // entry d (< R) of v after the rotation
+  int j, partner;
+  bool first;
+  if (interleaved) { j = d >> 1; first = !(d & 1); partner = first ? d + 1 : d - 1; }
+  else { const int half = R >> 1; first = d < half; j = first ? d : d - half; partner = first ? d + half : d - half; }
+  float sn, cs;
+  sincosf(pos * inv_freq[j], &sn, &cs);
+  return first ? v[d] * cs - v[partner] * sn : v[d] * cs + v[partner] * sn;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
+    const T* __restrict__ proj, int ld, int dq_off, int q_rank, const float* __restrict__ w_q, int dkv_off, int kv_rank,
+    int rot, const float* __restrict__ w_kv, float eps, const float* __restrict__ inv_freq, int interleaved,
+    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, T* __restrict__ cq, T* __restrict__ k_pages,
+    const int* __restrict__ page_table, int max_pages, int page_size) {
+  extern __shared__ __align__(16) float buf[];   // [rot]
+  __shared__ float scratch[33];
+  const int n = blockIdx.x;
+  const int slot = tok_slot[n];
+  const T* row = proj + (size_t)n * ld;
+  if (q_rank > 0) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < q_rank; c += PREP_THREADS) { const float v = to_f32<T>(row[dq_off + c]); ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += PREP_THREADS)
+      cq[(size_t)n * q_rank + c] = from_f32<T>(to_f32<T>(row[dq_off + c]) * inv * w_q[c]);
+  }
+  if (slot < 0 || !k_pages) return;
+  const int pos = tok_pos[n];
+  const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+  T* dst = k_pages + ((size_t)page * page_size + pos % page_size) * (kv_rank + rot);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < kv_rank; c += PREP_THREADS) { const float v = to_f32<T>(row[dkv_off + c]); ss = fmaf(v, v, ss); }
+  for (int c = threadIdx.x; c < rot; c += PREP_THREADS) buf[c] = to_f32<T>(row[dkv_off + kv_rank + c]);
+  ss = block_sum(ss, scratch);   // also orders buf
+  const float inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
+  for (int c = threadIdx.x; c < kv_rank; c += PREP_THREADS) dst[c] = from_f32<T>(to_f32<T>(row[dkv_off + c]) * inv * w_kv[c]);
+  for (int c = threadIdx.x; c < rot; c += PREP_THREADS)
+    dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq));
+}
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
+    const float* __restrict__ q_lat, const T* __restrict__ q, int q_stride, int q_rot_off, const T* __restrict__ k_pages,
+    const int* __restrict__ page_table, int max_pages, int page_size, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int interleaved, T* __restrict__ o_lat, int n_tokens,
+    int H, int kv_rank, int rot, float scale, int window) {
+  extern __shared__ __align__(16) float sm[];
+  const int Dk = kv_rank + rot, Dp = Dk + 1;
+  float* tile = sm;                                  // [KT][Dp]
+  float* qs_all = tile + (size_t)KT * Dp;            // [HPB][Dk]
+  float* raw = qs_all + (size_t)HPB * Dk;            // [HPB][rot]
+  const int n = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hd = blockIdx.y * HPB + warp;
+  const int slot = tok_slot[n];
+  if (slot < 0) return;
+  const int pos = tok_pos[n];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const bool live = hd < H;
+  float* qs = qs_all + (size_t)warp * Dk;
+  if (live) {
+    const float* ql = q_lat + ((size_t)hd * n_tokens + n) * kv_rank;
+    for (int d = lane; d < kv_rank; d += 32) qs[d] = ql[d] * scale;
+    const T* qr = q + ((size_t)n * H + hd) * q_stride + q_rot_off;
+    float* rw = raw + (size_t)warp * rot;
+    for (int d = lane; d < rot; d += 32) rw[d] = to_f32<T>(qr[d]);
+    __syncwarp();
+    for (int d = lane; d < rot; d += 32) qs[kv_rank + d] = rotated(rw, d, rot, interleaved != 0, (float)pos, inv_freq) * scale;
+  }
+  float m = -INFINITY, l = 0.f;
+  float acc[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+  const int* pt = page_table + (size_t)slot * max_pages;
+  for (int j0 = lo; j0 <= pos; j0 += KT) {
+    const int cnt = min(KT, pos - j0 + 1);
+    __syncthreads();   // the tile before is used up (and, the first time, qs is written)
+    for (int kk = warp; kk < cnt; kk += HPB) {
+      const int j = j0 + kk;
+      const T* src = k_pages + ((size_t)pt[j / page_size] * page_size + j % page_size) * Dk;
+      for (int d = lane; d < Dk; d += 32) tile[kk * Dp + d] = to_f32<T>(src[d]);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < cnt) {
+      const float* kr = tile + lane * Dp;
+      float a = 0.f;
+      for (int d = 0; d < Dk; ++d) a = fmaf(qs[d], kr[d], a);
+      s = a;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = lane < cnt ? expf(s - m_new) : 0.f;
+    const float corr = expf(m - m_new);   // 0 the first time (m = -inf)
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] *= corr;
+    for (int kk = 0; kk < cnt; ++kk) {
+      const float pk = __shfl_sync(0xffffffffu, p, kk);
+      const float* kr = tile + kk * Dp;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < kv_rank) acc[r] = fmaf(pk, kr[d], acc[r]);
+      }
+    }
+    m = m_new;
+  }
+  if (!live) return;
+  T* dst = o_lat + ((size_t)hd * n_tokens + n) * kv_rank;
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const int d = lane + 32 * r;
+    if (d < kv_rank) dst[d] = from_f32<T>(acc[r] * inv);
+  }
+}
+
+template <typename T>
+__global__ void head_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_ld, T* __restrict__ out,
+                                 int n_tokens, int H, int vdim) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * H * vdim) return;
+  const int v = (int)(i % vdim);
+  const int hd = (int)((i / vdim) % H);
+  const size_t n = i / ((size_t)vdim * H);
+  float val = o[((size_t)hd * n_tokens + n) * vdim + v];
+  if (gate) {
+    const float g = to_f32<T>(gate[n * gate_ld + hd]);
+    val *= 1.f / (1.f + expf(-g));
+  }
+  out[i] = from_f32<T>(val);
+}
+
+template <typename K> int opt_in(K kernel, size_t bytes) {
+  if (bytes > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+template <typename T, int NR>
+int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, const void* k_pages, const int* page_table,
+                int max_pages, int page_size, const int* tok_slot, const int* tok_pos, const float* inv_freq, int interleaved,
+                void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+  const int Dk = kv_rank + rot;
+  const size_t smem = sizeof(float) * ((size_t)KT * (Dk + 1) + (size_t)HPB * Dk + (size_t)HPB * rot);
+  int rc = opt_in(latent_attn_rows_kernel<T, NR>, smem);
+  if (rc) return rc;
+  dim3 grid(n_tokens, (H + HPB - 1) / HPB);
+  latent_attn_rows_kernel<T, NR><<<grid, HPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
+                                                               max_pages, page_size, tok_slot, tok_pos, inv_freq, interleaved,
+                                                               (T*)o_lat, n_tokens, H, kv_rank, rot, scale, window);
+  return launch_status();
+}
+}  // namespace
+
+DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_off, int q_rank, const float* w_q, int dkv_off,
+                                int kv_rank, int rot, const float* w_kv, float eps, const float* inv_freq, int interleaved,
+                                const int* tok_slot, const int* tok_pos, void* cq, void* k_pages, const int* page_table,
+                                int max_pages, int page_size, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (kv_rank <= 0 || rot < 0 || (rot & 1)) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const size_t smem = sizeof(float) * (size_t)(rot > 0 ? rot : 1);
+  if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (is_bf16)
+    latent_prep_kernel<bf><<<n, PREP_THREADS, smem, st>>>((const bf*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv, eps,
+                                                          inv_freq, interleaved, tok_slot, tok_pos, (bf*)cq, (bf*)k_pages, page_table,
+                                                          max_pages, page_size);
+  else
+    latent_prep_kernel<float><<<n, PREP_THREADS, smem, st>>>((const float*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv,
+                                                             eps, inv_freq, interleaved, tok_slot, tok_pos, (float*)cq, (float*)k_pages,
+                                                             page_table, max_pages, page_size);
+  return launch_status();
+}
+
+DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void* q, int q_stride, int q_rot_off,
+                                     const void* k_pages, const int* page_table, int max_pages, int page_size,
+                                     const int* tok_slot, const int* tok_pos, const float* inv_freq, int interleaved, void* o_lat,
+                                     int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (kv_rank <= 0 || kv_rank > 512 || rot < 0 || (rot & 1) || H <= 0 || (H + HPB - 1) / HPB > 65535) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int nr = (kv_rank + 31) / 32;
+#define DRYFT_LATENT_ROWS(NR)                                                                                                      \
+  return is_bf16 ? launch_rows<bf, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot, tok_pos,  \
+                                       inv_freq, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)                \
+                 : launch_rows<float, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot,      \
+                                          tok_pos, inv_freq, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)
+  if (nr <= 1) { DRYFT_LATENT_ROWS(1); }
+  if (nr <= 2) { DRYFT_LATENT_ROWS(2); }
+  if (nr <= 4) { DRYFT_LATENT_ROWS(4); }
+  if (nr <= 8) { DRYFT_LATENT_ROWS(8); }
+  DRYFT_LATENT_ROWS(16);
+#undef DRYFT_LATENT_ROWS
+}
+
+DRYFT_API int dryft_head_gate(int is_bf16, const float* o, const void* gate, int gate_ld, void* out, int n_tokens, int H, int vdim,
+                              cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  typedef __nv_bfloat16 bf;
+  const size_t total = (size_t)n_tokens * H * vdim;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (is_bf16) head_gate_kernel<bf><<<blocks, 256, 0, st>>>(o, (const bf*)gate, gate_ld, (bf*)out, n_tokens, H, vdim);
+  else head_gate_kernel<float><<<blocks, 256, 0, st>>>(o, (const float*)gate, gate_ld, (float*)out, n_tokens, H, vdim);
+  return launch_status();
+}

@@ -1,0 +1,271 @@
+// Mixers whose memory is a fixed-size 32-bit state per sequence instead of cached keys: a step runs the tokens it is
+// given from the state the step before left, and leaves the state for the next (one token, a prompt, or a piece of one).
+//
+// retention_scan     linear attention with one fixed decay per head, no softmax and no denominator.  Per head, with the
+//                    rotated query q_t, the rotated key k_t times k_scale, and the value v_t of token t:
+//                        S_t = decay * S_(t-1) + k_t v_t^T          S [dim, vdim], 32-bit
+//                        o_t = S_t^T q_t ;  o_t <- o_t / sqrt(mean(o_t^2) + eps) ;  out = T( o_t * silu(g_t) )
+//                    One block per (sequence, head) walks the sequence's tokens in order with S in shared memory.
+//                    q | k | v | g are columns of one projection row (offsets given); the rotation pairs entry i with
+//                    entry i + R/2 of the first R entries (angle = position * inv_freq[i], 32-bit).
+//
+// rglru_gates        the input side of a real-gated linear recurrent unit over C channels in `blocks` equal groups:
+//                        x_t  = xproj_t + x_bias                                   (a column range of the projection row)
+//                        u_t  = conv_b + sum_j conv_w[c][j] * x_(t - (taps-1) + j)    (causal, per channel; inputs before
+//                               the step come from the sequence's stored tail, zeros before the sequence's start)
+//                        r_t  = sigmoid(Wa[b] u_t,b + ba) ;  i_t = sigmoid(Wi[b] u_t,b + bi)     (per group b, 32-bit)
+//                        log a_t = -c * r_t * softplus(lam) ;  a_t = exp(log a_t)
+//                        b_t  = sqrt(1 - a_t^2) * i_t * u_t          (1 - a^2 as -expm1(2 log a): no cancellation)
+//                    leaves a_t and b_t [tokens, C] in 32-bit.
+// rglru_scan         S_t = a_t * S_(t-1) + b_t per channel, out_t = T( S_t * gelu_tanh(yproj_t + y_bias) ), then the new
+//                    state and the new tail (the last taps-1 inputs) are stored.
+//
+// Everything that enters a recurrence is 32-bit whatever the activation type T.  Sizes are runtime arguments of any value
+// (shared memory permitting).  No block waits on another.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int RT_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
+    const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int g_off, const int* __restrict__ cu_q,
+    const int* __restrict__ seq_slot, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int rot,
+    const float* __restrict__ decay, float* __restrict__ state, T* __restrict__ out, int H, int dim, int vdim,
+    float k_scale, float eps) {
+  extern __shared__ __align__(16) float smem[];
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  const int n0 = cu_q[b], n1 = cu_q[b + 1];
+  const int cols = vdim < RT_THREADS ? vdim : RT_THREADS;   // threads side by side over the value index
+  const int groups = RT_THREADS / cols;                      // groups of them over the key index
+  float* S = smem;                        // [dim][vdim]
+  float* qs = S + (size_t)dim * vdim;     // [dim]
+  float* ks = qs + dim;                   // [dim]
+  float* vs = ks + dim;                   // [vdim]
+  float* red = vs + vdim;                 // [groups][vdim]
+  __shared__ float scratch[33];
+  const int tid = threadIdx.x;
+  float* Sg = state + ((size_t)slot * H + hd) * dim * vdim;
+  for (int i = tid; i < dim * vdim; i += RT_THREADS) S[i] = Sg[i];
+  const float dec = decay[hd];
+  const int half = rot >> 1;
+  const int cv = tid % cols, rg = tid / cols;
+  const bool active = rg < groups;
+  for (int n = n0; n < n1; ++n) {
+    const T* row = proj + (size_t)n * ld;
+    const float pos = (float)tok_pos[n];
+    __syncthreads();   // the token before is done with qs / ks / vs / red
+    for (int i = tid; i < 2 * dim; i += RT_THREADS) {
+      const bool is_k = i >= dim;
+      const int d = is_k ? i - dim : i;
+      const T* src = row + (is_k ? k_off : q_off) + hd * dim;
+      float val = to_f32<T>(src[d]);
+      if (d < rot) {
+        const int j = d < half ? d : d - half;
+        const float other = to_f32<T>(src[d < half ? d + half : d - half]);
+        float sn, cs;
+        sincosf(pos * inv_freq[j], &sn, &cs);
+        val = d < half ? val * cs - other * sn : val * cs + other * sn;
+      }
+      if (is_k) ks[d] = val * k_scale; else qs[d] = val;
+    }
+    for (int i = tid; i < vdim; i += RT_THREADS) vs[i] = to_f32<T>(row[v_off + hd * vdim + i]);
+    __syncthreads();
+    if (active) {
+      for (int v = cv; v < vdim; v += cols) {
+        const float vv = vs[v];
+        float acc = 0.f;
+        for (int d = rg; d < dim; d += groups) {
+          const float s = fmaf(dec, S[d * vdim + v], ks[d] * vv);
+          S[d * vdim + v] = s;
+          acc = fmaf(s, qs[d], acc);
+        }
+        red[rg * vdim + v] = acc;
+      }
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int v = tid; v < vdim; v += RT_THREADS) {
+      float o = 0.f;
+      for (int g = 0; g < groups; ++g) o += red[g * vdim + v];
+      vs[v] = o;          // vs is free again: every thread passed the barrier above
+      ss = fmaf(o, o, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)vdim + eps);
+    for (int v = tid; v < vdim; v += RT_THREADS) {
+      const float g = to_f32<T>(row[g_off + hd * vdim + v]);
+      out[(size_t)n * H * vdim + hd * vdim + v] = from_f32<T>(vs[v] * inv * (g / (1.f + expf(-g))));
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * vdim; i += RT_THREADS) Sg[i] = S[i];
+}
+
+constexpr int GT = 8;          // tokens per block of rglru_gates
+constexpr int G_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(G_THREADS) rglru_gates_kernel(
+    const T* __restrict__ proj, int ld, int x_off, const float* __restrict__ x_bias, const int* __restrict__ tok_slot,
+    const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps, const float* __restrict__ tail,
+    const float* __restrict__ w_gates, const float* __restrict__ b_a, const float* __restrict__ b_i,
+    const float* __restrict__ sp_lam, float c_mult, float* __restrict__ a_out, float* __restrict__ b_out, int n_tokens,
+    int C, int nb) {
+  extern __shared__ __align__(16) float u_s[];   // [GT][nb]
+  const int n0 = blockIdx.x * GT, blk = blockIdx.y, c0 = blk * nb;
+  const int K1 = taps - 1;
+  for (int idx = threadIdx.x; idx < GT * nb; idx += G_THREADS) {
+    const int t = idx / nb, cc = idx % nb, n = n0 + t, c = c0 + cc;
+    float u = 0.f;
+    if (n < n_tokens) {
+      const int slot = tok_slot[n];
+      if (slot >= 0) {
+        int avail = 0;   // tokens of the same sequence right before this one in the step, up to taps-1
+        while (avail < K1 && n - avail - 1 >= 0 && tok_slot[n - avail - 1] == slot) ++avail;
+        u = conv_b[c];
+        for (int j = 0; j < taps; ++j) {
+          const int back = K1 - j;
+          float xv;
+          if (back <= avail) xv = to_f32<T>(proj[(size_t)(n - back) * ld + x_off + c]) + x_bias[c];
+          else xv = tail[((size_t)slot * K1 + (K1 - back + avail)) * C + c];
+          u = fmaf(conv_w[(size_t)c * taps + j], xv, u);
+        }
+      }
+    }
+    u_s[t * nb + cc] = u;
+  }
+  __syncthreads();
+  const float* wg = w_gates + (size_t)blk * nb * 2 * nb;   // [k][2][o]
+  for (int o = threadIdx.x; o < nb; o += G_THREADS) {
+    float ar[GT], ai[GT];
+    const float ba = b_a[c0 + o], bi = b_i[c0 + o];
+#pragma unroll
+    for (int t = 0; t < GT; ++t) { ar[t] = ba; ai[t] = bi; }
+    for (int k = 0; k < nb; ++k) {
+      const float wr = wg[((size_t)k * 2) * nb + o], wi = wg[((size_t)k * 2 + 1) * nb + o];
+#pragma unroll
+      for (int t = 0; t < GT; ++t) {
+        const float uv = u_s[t * nb + k];
+        ar[t] = fmaf(wr, uv, ar[t]);
+        ai[t] = fmaf(wi, uv, ai[t]);
+      }
+    }
+    const float sp = sp_lam[c0 + o];
+#pragma unroll
+    for (int t = 0; t < GT; ++t) {
+      const int n = n0 + t;
+      if (n >= n_tokens) break;
+      const float r = 1.f / (1.f + expf(-ar[t])), ig = 1.f / (1.f + expf(-ai[t]));
+      const float log_a = -c_mult * r * sp;
+      a_out[(size_t)n * C + c0 + o] = expf(log_a);
+      b_out[(size_t)n * C + c0 + o] = sqrtf(-expm1f(2.f * log_a)) * ig * u_s[t * nb + o];
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void rglru_scan_kernel(const T* __restrict__ proj, int ld, int y_off, const float* __restrict__ y_bias, int x_off,
+                                  const float* __restrict__ x_bias, const int* __restrict__ cu_q,
+                                  const int* __restrict__ seq_slot, const float* __restrict__ a_in,
+                                  const float* __restrict__ b_in, float* __restrict__ state, float* __restrict__ tail, int taps,
+                                  T* __restrict__ out, int C) {
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int slot = seq_slot[b];
+  if (slot < 0 || c >= C) return;
+  const int n0 = cu_q[b], n1 = cu_q[b + 1];
+  float S = state[(size_t)slot * C + c];
+  const float yb = y_bias[c];
+  for (int n = n0; n < n1; ++n) {
+    S = fmaf(a_in[(size_t)n * C + c], S, b_in[(size_t)n * C + c]);
+    const float yv = gelu_tanh_f(to_f32<T>(proj[(size_t)n * ld + y_off + c]) + yb);
+    out[(size_t)n * C + c] = from_f32<T>(S * yv);
+  }
+  state[(size_t)slot * C + c] = S;
+  const int K1 = taps - 1, q = n1 - n0;
+  const float xb = x_bias[c];
+  for (int j = 0; j < K1; ++j) {   // ascending: an old entry is read before the entry below it is overwritten
+    const int idx = q - K1 + j;
+    float* dst = tail + ((size_t)slot * K1 + j) * C + c;
+    if (idx >= 0) *dst = to_f32<T>(proj[(size_t)(n0 + idx) * ld + x_off + c]) + xb;
+    else *dst = tail[((size_t)slot * K1 + j + q) * C + c];
+  }
+}
+
+template <typename K> int opt_in_smem(K kernel, size_t bytes) {
+  if (bytes > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+}  // namespace
+
+DRYFT_API int dryft_retention_scan(int is_bf16, const void* proj, int ld, int q_off, int k_off, int v_off, int g_off,
+                                   const int* cu_q, const int* seq_slot, const int* tok_pos, const float* inv_freq, int rot,
+                                   const float* decay, float* state, void* out, int n_seqs, int H, int dim, int vdim,
+                                   float k_scale, float eps, cudaStream_t st) {
+  if (n_seqs <= 0) return 0;
+  if (H <= 0 || dim <= 0 || vdim <= 0 || rot < 0 || rot > dim || (rot & 1) || H > 65535) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int cols = vdim < RT_THREADS ? vdim : RT_THREADS, groups = RT_THREADS / cols;
+  const size_t smem = sizeof(float) * ((size_t)dim * vdim + 2 * (size_t)dim + vdim + (size_t)groups * vdim);
+  int rc = is_bf16 ? opt_in_smem(retention_scan_kernel<bf>, smem) : opt_in_smem(retention_scan_kernel<float>, smem);
+  if (rc) return rc;
+  dim3 grid(n_seqs, H);
+  if (is_bf16)
+    retention_scan_kernel<bf><<<grid, RT_THREADS, smem, st>>>((const bf*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot, tok_pos,
+                                                              inv_freq, rot, decay, state, (bf*)out, H, dim, vdim, k_scale, eps);
+  else
+    retention_scan_kernel<float><<<grid, RT_THREADS, smem, st>>>((const float*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot,
+                                                                 tok_pos, inv_freq, rot, decay, state, (float*)out, H, dim, vdim,
+                                                                 k_scale, eps);
+  return launch_status();
+}
+
+DRYFT_API int dryft_rglru_gates(int is_bf16, const void* proj, int ld, int x_off, const float* x_bias, const int* tok_slot,
+                                const float* conv_w, const float* conv_b, int taps, const float* tail, const float* w_gates,
+                                const float* b_a, const float* b_i, const float* sp_lam, float c_mult, float* a_out, float* b_out,
+                                int n_tokens, int C, int n_blocks, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (taps < 1 || n_blocks < 1 || C % n_blocks || n_blocks > 65535) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int nb = C / n_blocks;
+  const size_t smem = sizeof(float) * (size_t)GT * nb;
+  int rc = is_bf16 ? opt_in_smem(rglru_gates_kernel<bf>, smem) : opt_in_smem(rglru_gates_kernel<float>, smem);
+  if (rc) return rc;
+  dim3 grid((n_tokens + GT - 1) / GT, n_blocks);
+  if (is_bf16)
+    rglru_gates_kernel<bf><<<grid, G_THREADS, smem, st>>>((const bf*)proj, ld, x_off, x_bias, tok_slot, conv_w, conv_b, taps, tail,
+                                                          w_gates, b_a, b_i, sp_lam, c_mult, a_out, b_out, n_tokens, C, nb);
+  else
+    rglru_gates_kernel<float><<<grid, G_THREADS, smem, st>>>((const float*)proj, ld, x_off, x_bias, tok_slot, conv_w, conv_b, taps,
+                                                             tail, w_gates, b_a, b_i, sp_lam, c_mult, a_out, b_out, n_tokens, C, nb);
+  return launch_status();
+}
+
+DRYFT_API int dryft_rglru_scan(int is_bf16, const void* proj, int ld, int y_off, const float* y_bias, int x_off,
+                               const float* x_bias, const int* cu_q, const int* seq_slot, const float* a_in, const float* b_in,
+                               float* state, float* tail, int taps, void* out, int n_seqs, int C, cudaStream_t st) {
+  if (n_seqs <= 0) return 0;
+  typedef __nv_bfloat16 bf;
+  const int threads = 128;
+  dim3 grid(n_seqs, (C + threads - 1) / threads);
+  if (grid.y > 65535) return DRYFT_ERR_UNSUPPORTED;
+  if (is_bf16)
+    rglru_scan_kernel<bf><<<grid, threads, 0, st>>>((const bf*)proj, ld, y_off, y_bias, x_off, x_bias, cu_q, seq_slot, a_in, b_in, state,
+                                                    tail, taps, (bf*)out, C);
+  else
+    rglru_scan_kernel<float><<<grid, threads, 0, st>>>((const float*)proj, ld, y_off, y_bias, x_off, x_bias, cu_q, seq_slot, a_in, b_in,
+                                                       state, tail, taps, (float*)out, C);
+  return launch_status();
+}

@@ -1,0 +1,225 @@
+// A 32-bit residual stream that is kept as several copies ("streams") joined by small learned matrices
+// (hyper-connections), the embedding that starts it, and the clamped gated activation of its feed-forward.
+//
+//   embed_pair_norm   x32[n] = norm( table[token] * scale + pair_table[row] ) * w,  row = (prev * mul_prev + token * mul_cur)
+//                     mod buckets, or `buckets` (the table's last row) for a sequence's first token.  `prev` is the token
+//                     before it in the step, or -- for the first token a sequence brings in a step -- the sequence's
+//                     stored last token.  Both the pair table and the norm are optional.
+//   seq_last_token    prev_state[slot] = the last token each sequence brought in this step
+//   hc_step           with S streams x_1..x_S per row (32-bit), an optional pending sublayer output y and the next
+//                     sublayer's input weights:
+//                         x'_t = sum_s mix[s][t] * x_s + mult * out[t] * y          (all t at once from the old x)
+//                         u    = sum_t in[t] * x'_t ;  h = T( u / sqrt(mean(u^2) + eps) * w )
+//                     either half may be left out; the input may hold one stream that stands for all S (the start);
+//                     with `rows` only the gathered rows are read and nothing is written back (the last norm).
+//                     S = 1 with mix = out = in = 1 is the plain pre-norm residual  x += mult * y ; h = norm(x).
+//   glu_clamp         out = g * sigmoid(alpha * g) * (u + up_offset),  g = min(gate, limit), u = clamp(up, -limit, limit)
+//
+// Sums, norms and the streams are 32-bit whatever the activation type T.  One block per row; widths are runtime
+// arguments of any size.  No block waits on another.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int THREADS = 256;
+constexpr int MAX_STREAMS = 8;
+
+template <typename TT>
+__global__ void __launch_bounds__(THREADS) embed_pair_norm_kernel(
+    const int* __restrict__ tokens, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+    const int* __restrict__ prev_state, const TT* __restrict__ table, const TT* __restrict__ pair_table, int buckets,
+    long long mul_prev, long long mul_cur, float scale, const float* __restrict__ norm_w, float eps,
+    float* __restrict__ x32, int width, int vocab, int* __restrict__ err) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[33];
+  const int n = blockIdx.x;
+  const int slot = tok_slot[n];
+  const int tok = tokens[n];
+  const bool bad = tok < 0 || tok >= vocab;
+  if (slot < 0 || bad) {  // a padding row, or an id outside the table: the row is zero
+    if (slot >= 0 && threadIdx.x == 0 && err) atomicExch(err, 1);
+    for (int c = threadIdx.x; c < width; c += THREADS) x32[(size_t)n * width + c] = 0.f;
+    return;
+  }
+  const TT* pair = nullptr;
+  if (pair_table) {
+    long long r = buckets;
+    if (n > 0 && tok_slot[n - 1] == slot) {
+      r = ((long long)tokens[n - 1] * mul_prev + (long long)tok * mul_cur) % buckets;
+    } else if (tok_pos[n] > 0) {
+      r = ((long long)prev_state[slot] * mul_prev + (long long)tok * mul_cur) % buckets;
+    }
+    if (r < 0) r += buckets;
+    pair = pair_table + (size_t)r * width;
+  }
+  const TT* src = table + (size_t)tok * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += THREADS) {
+    float v = to_f32<TT>(src[c]) * scale;
+    if (pair) v += to_f32<TT>(pair[c]);
+    row[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (!norm_w) {
+    for (int c = threadIdx.x; c < width; c += THREADS) x32[(size_t)n * width + c] = row[c];
+    return;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += THREADS) x32[(size_t)n * width + c] = row[c] * inv * norm_w[c];
+}
+
+__global__ void seq_last_token_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_slot, int n_tokens,
+                                      int* __restrict__ prev_state) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= n_tokens) return;
+  const int slot = tok_slot[n];
+  if (slot < 0) return;
+  if (n + 1 == n_tokens || tok_slot[n + 1] != slot) prev_state[slot] = tokens[n];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) hc_step_kernel(
+    const float* __restrict__ x_in, int s_in, float* __restrict__ x_out, int S, const T* __restrict__ y,
+    const float* __restrict__ mix, const float* __restrict__ outw, float mult, const float* __restrict__ inw,
+    const float* __restrict__ norm_w, float eps, const int* __restrict__ rows, T* __restrict__ h, int width) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[33];
+  __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = y ? mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    c_out[threadIdx.x] = y ? mult * outw[threadIdx.x] : 0.f;
+    c_in[threadIdx.x] = inw ? inw[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += THREADS) {
+    float x[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; ++s)
+      if (s < S) x[s] = x_in[(src * s_in + (s_in == 1 ? 0 : s)) * width + c];
+    if (y) {
+      const float yv = to_f32<T>(y[src * width + c]);
+      float xn[MAX_STREAMS];
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t) {
+        if (t < S) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < MAX_STREAMS; ++s)
+            if (s < S) acc = fmaf(c_mix[s * S + t], x[s], acc);
+          xn[t] = fmaf(c_out[t], yv, acc);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t)
+        if (t < S) x[t] = xn[t];
+    }
+    if (x_out) {
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t)
+        if (t < S) x_out[(src * S + t) * width + c] = x[t];
+    }
+    if (inw) {
+      float u = 0.f;
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t)
+        if (t < S) u = fmaf(c_in[t], x[t], u);
+      row[c] = u;
+      ss = fmaf(u, u, ss);
+    }
+  }
+  if (!inw) return;
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += THREADS) h[(size_t)r * width + c] = from_f32<T>(row[c] * inv * norm_w[c]);
+}
+
+template <typename T>
+__global__ void glu_clamp_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, float limit,
+                                 int has_limit, float alpha, float up_offset) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * inter) return;
+  const size_t r = i / inter, f = i % inter;
+  float g = to_f32<T>(gate_up[r * 2 * inter + f]);
+  float u = to_f32<T>(gate_up[r * 2 * inter + inter + f]);
+  if (has_limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  const float act = g / (1.f + expf(-alpha * g));
+  out[i] = from_f32<T>(act * (u + up_offset));
+}
+
+template <typename K> int row_smem(K kernel, int width) {
+  const size_t bytes = sizeof(float) * (size_t)width;
+  if (bytes > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+}  // namespace
+
+DRYFT_API int dryft_embed_pair_norm(int table_bf16, const int* tokens, const int* tok_slot, const int* tok_pos,
+                                    const int* prev_state, const void* table, const void* pair_table, int buckets,
+                                    long long mul_prev, long long mul_cur, float scale, const float* norm_w, float eps, float* x32,
+                                    int n, int width, int vocab, int* err, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (pair_table && (buckets <= 0 || !prev_state)) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const size_t smem = sizeof(float) * (size_t)width;
+  int rc = table_bf16 ? row_smem(embed_pair_norm_kernel<bf>, width) : row_smem(embed_pair_norm_kernel<float>, width);
+  if (rc) return rc;
+  if (table_bf16)
+    embed_pair_norm_kernel<bf><<<n, THREADS, smem, st>>>(tokens, tok_slot, tok_pos, prev_state, (const bf*)table, (const bf*)pair_table,
+                                                         buckets, mul_prev, mul_cur, scale, norm_w, eps, x32, width, vocab, err);
+  else
+    embed_pair_norm_kernel<float><<<n, THREADS, smem, st>>>(tokens, tok_slot, tok_pos, prev_state, (const float*)table,
+                                                            (const float*)pair_table, buckets, mul_prev, mul_cur, scale, norm_w, eps,
+                                                            x32, width, vocab, err);
+  return launch_status();
+}
+
+DRYFT_API int dryft_seq_last_token(const int* tokens, const int* tok_slot, int n, int* prev_state, cudaStream_t st) {
+  if (n <= 0) return 0;
+  seq_last_token_kernel<<<(n + 255) / 256, 256, 0, st>>>(tokens, tok_slot, n, prev_state);
+  return launch_status();
+}
+
+DRYFT_API int dryft_hc_step(int is_bf16, const float* x_in, int s_in, float* x_out, int n_streams, const void* y, const float* mix,
+                            const float* outw, float mult, const float* inw, const float* norm_w, float eps, const int* rows,
+                            void* h, int n_rows, int width, cudaStream_t st) {
+  if (n_rows <= 0) return 0;
+  if (n_streams < 1 || n_streams > MAX_STREAMS || (s_in != 1 && s_in != n_streams)) return DRYFT_ERR_UNSUPPORTED;
+  if (y && (!mix || !outw)) return DRYFT_ERR_UNSUPPORTED;
+  if (inw && (!norm_w || !h)) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const size_t smem = sizeof(float) * (size_t)width;
+  int rc = is_bf16 ? row_smem(hc_step_kernel<bf>, width) : row_smem(hc_step_kernel<float>, width);
+  if (rc) return rc;
+  if (is_bf16)
+    hc_step_kernel<bf><<<n_rows, THREADS, smem, st>>>(x_in, s_in, x_out, n_streams, (const bf*)y, mix, outw, mult, inw, norm_w, eps,
+                                                      rows, (bf*)h, width);
+  else
+    hc_step_kernel<float><<<n_rows, THREADS, smem, st>>>(x_in, s_in, x_out, n_streams, (const float*)y, mix, outw, mult, inw, norm_w,
+                                                         eps, rows, (float*)h, width);
+  return launch_status();
+}
+
+DRYFT_API int dryft_glu_clamp(int is_bf16, const void* gate_up, void* out, int rows, int inter, float limit, int has_limit,
+                              float alpha, float up_offset, cudaStream_t st) {
+  if (rows <= 0 || inter <= 0) return 0;
+  typedef __nv_bfloat16 bf;
+  const size_t total = (size_t)rows * inter;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (is_bf16)
+    glu_clamp_kernel<bf><<<blocks, 256, 0, st>>>((const bf*)gate_up, (bf*)out, rows, inter, limit, has_limit, alpha, up_offset);
+  else
+    glu_clamp_kernel<float><<<blocks, 256, 0, st>>>((const float*)gate_up, (float*)out, rows, inter, limit, has_limit, alpha,
+                                                    up_offset);
+  return launch_status();
+}

@@ -126,7 +126,8 @@ class Engine:
             self.max_tokens = opts.max_tokens or self.max_batch * _round_up(self.max_seq_len, opts.page_size)
             needs, borrow = self.model.cache_needs()
             self.cache = SequenceCache(needs, borrow, max_tokens=self.max_tokens, max_slots=self.max_batch,
-                                       max_seq_len=self.max_seq_len, page_size=opts.page_size, dtype=dtype, device=dev)
+                                       max_seq_len=self.max_seq_len, page_size=opts.page_size, dtype=dtype, device=dev,
+                                       named_states=self.model.named_state_needs())
             self.stepper = Stepper(self.model, self.cache, self.rt, cuda_graphs=opts.cuda_graphs)
         self._backend = _DeviceBackend(self)
 

@@ -37,6 +37,8 @@ class DecoderModel:
             extra = {e.name: FAMILIES[e.family].get(e.spec.kind)(e.spec.params, e.prefix, weights, rt) for e in layer.extra}
             make = BLOCKS.get(layer.block)
             self.blocks.append(make(norm_mixer, mixer, norm_ffn, ffn, extra=extra) if extra else make(norm_mixer, mixer, norm_ffn, ffn))
+        # a test or a bring-up script may watch the stream: called as layer_tap(run step, block, Residual) after every block
+        self.layer_tap = None
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, weights, rt)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, spec.head_prefix, weights, rt, embedding=self.embedding)
 
@@ -48,6 +50,12 @@ class DecoderModel:
             needs.append((mixer.kv_need(), mixer.state_need()))
             borrow.append(st.cache_from)
         return needs, borrow
+
+    def named_state_needs(self) -> dict:
+        """Per-sequence state of the parts outside the layers: ``{name: StateNeed}`` (today: the embedding's)."""
+        need = getattr(self.embedding, "state_need", None)
+        need = need() if callable(need) else None
+        return {"embedding": need} if need is not None else {}
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -71,7 +79,9 @@ class DecoderModel:
         """Run the step's tokens through every run step; logits ``[n_want, vocab]`` float32 at the
         packed rows ``want_rows`` (None if nothing is wanted).  ``all_rows`` says that ``want_rows`` is simply
         every row in order (a decode step), which lets the head take the fused path."""
-        if getattr(self.embedding, "takes_context", False):   # an embedding that adds the tokens' positions
+        if getattr(self.embedding, "takes_state", False):     # an embedding that remembers each sequence's last token
+            res = self.embedding.forward(ctx.tokens, ctx.n_tokens, ctx, cache.named_state("embedding"))
+        elif getattr(self.embedding, "takes_context", False):   # an embedding that adds the tokens' positions
             res = self.embedding.forward(ctx.tokens, ctx.n_tokens, ctx)
         else:
             res = self.embedding.forward(ctx.tokens, ctx.n_tokens)
@@ -86,8 +96,12 @@ class DecoderModel:
                 res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None, next_norm=nxt)
             else:
                 res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
+            if self.layer_tap is not None:
+                self.layer_tap(i, block, res)
         if n_want == 0:
             return None
+        if res.closer is not None:   # streams that only their block arrangement knows how to join
+            return self.head.forward(res.closer.final_rows(res, self.final_norm, want_rows, n_want))
         if (all_rows and res.delta is None and res.ss is not None and hasattr(self.head, "forward_normed")
                 and self.head.can_fuse(res.x.shape[0], self.final_norm)):
             xw = res.xw if res.xw_norm is self.final_norm else None

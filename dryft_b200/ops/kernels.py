@@ -1186,3 +1186,273 @@ def sample_rows(logits, temperature: float, top_k: int, seed: int, row_seq, row_
     _ok(core().dryft_sample_rows(_ptr(logits), rows, vocab, vocab, float(temperature), int(top_k), int(seed) & (2**64 - 1),
                                  _ptr(row_seq), _ptr(row_step), int(step_base), _ptr(out), _ptr(row_slot), _ptr(last_token),
                                  _stream()), "sample_rows")
+
+
+# ----------------------------------------------------------------------------- libraries built only for models that use them
+_single: Dict[str, ctypes.CDLL] = {}
+
+
+def _single_lib(name: str, protos: Dict[str, list]) -> ctypes.CDLL:
+    """A library made of one source file ``<name>.cu``, compiled the first time a model needs it."""
+    with _lock:
+        lib = _single.get(name)
+        if lib is None:
+            lib = _load(build.build_library(name, (name + ".cu",)))
+            for fn, argtypes in protos.items():
+                getattr(lib, fn).argtypes = argtypes
+                getattr(lib, fn).restype = _i
+            _single[name] = lib
+        return lib
+
+
+def stream_hc_lib() -> ctypes.CDLL:
+    """Several residual streams joined by small matrices, the embedding that starts them, the clamped gated activation."""
+    return _single_lib("stream_hc", {
+        "dryft_embed_pair_norm": [_i, _p, _p, _p, _p, _p, _p, _i, _ll, _ll, _f, _p, _f, _p, _i, _i, _i, _p, _p],
+        "dryft_seq_last_token": [_p, _p, _i, _p, _p],
+        "dryft_hc_step": [_i, _p, _i, _p, _i, _p, _p, _p, _f, _p, _p, _f, _p, _p, _i, _i, _p],
+        "dryft_glu_clamp": [_i, _p, _p, _i, _i, _f, _i, _f, _f, _p],
+    })
+
+
+def recurrent_lib() -> ctypes.CDLL:
+    """Mixers with a fixed-size 32-bit state per sequence: retention, gated linear recurrence."""
+    return _single_lib("recurrent", {
+        "dryft_retention_scan": [_i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p],
+        "dryft_rglru_gates": [_i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _f, _p, _p, _i, _i, _i, _p],
+        "dryft_rglru_scan": [_i, _p, _i, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p],
+    })
+
+
+def latent_attn_lib() -> ctypes.CDLL:
+    """Attention over cached low-rank latents."""
+    return _single_lib("latent_attn", {
+        "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
+        "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
+    })
+
+
+# ----------------------------------------------------------------------------- streams joined by small matrices
+HC_MAX_STREAMS = 8
+
+
+def embed_pair_norm(tokens, tok_slot, tok_pos, table, x32, *, scale: float = 1.0, pair_table=None, buckets: int = 0,
+                    mul_prev: int = 0, mul_cur: int = 0, prev_state=None, norm_w=None, eps: float = 0.0, err=None) -> None:
+    """``x32[n] = norm(table[tokens[n]] * scale + pair_table[row]) * norm_w`` (32-bit), ``row`` hashed from the token and the
+    one before it in its sequence (``prev_state[slot]`` for the first token a sequence brings in a step; the table's row
+    ``buckets`` for a sequence's first token).  Without ``pair_table`` nothing is added, without ``norm_w`` nothing normed."""
+    n, width = x32.shape
+    _need(x32, "stream", torch.float32)
+    for t, nm in ((tokens, "tokens"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+        if t.numel() < n:
+            raise KernelError(f"embed_pair_norm: {nm} shorter than the rows")
+    _need(table, "embedding table", None, (None, width))
+    if pair_table is not None:
+        _need(pair_table, "pair table", table.dtype, (buckets + 1, width))
+        _need(prev_state, "prev_state", torch.int32)
+    if norm_w is not None:
+        _need(norm_w, "norm weight", torch.float32, (width,))
+    if err is not None:
+        _need(err, "err", torch.int32)
+    _ok(stream_hc_lib().dryft_embed_pair_norm(_act(table, "embedding table"), _ptr(tokens), _ptr(tok_slot), _ptr(tok_pos),
+                                              _ptr(prev_state), _ptr(table), _ptr(pair_table), int(buckets), int(mul_prev),
+                                              int(mul_cur), float(scale), _ptr(norm_w), float(eps), _ptr(x32), n, width,
+                                              table.shape[0], _ptr(err), _stream()), f"embed_pair_norm (width {width})")
+
+
+def seq_last_token(tokens, tok_slot, n: int, prev_state) -> None:
+    """``prev_state[slot] =`` the last token each sequence brought in this step."""
+    for t, nm in ((tokens, "tokens"), (tok_slot, "tok_slot"), (prev_state, "prev_state")):
+        _need(t, nm, torch.int32)
+    _ok(stream_hc_lib().dryft_seq_last_token(_ptr(tokens), _ptr(tok_slot), n, _ptr(prev_state), _stream()), "seq_last_token")
+
+
+def hc_step(x_in, n_streams: int, *, x_out=None, y=None, mix=None, outw=None, mult: float = 1.0, inw=None, norm_w=None,
+            eps: float = 0.0, rows=None, h=None) -> None:
+    """One joint of a residual stream held as ``n_streams`` 32-bit copies.  ``x_in`` is ``[n, n_streams, W]`` or ``[n, W]``
+    (one copy standing for all).  With ``y [n, W]``: ``x'_t = sum_s mix[s, t] x_s + mult * outw[t] * y``; written to
+    ``x_out [n, n_streams, W]`` if given (may be ``x_in``).  With ``inw``: ``h = T(rmsnorm(sum_t inw[t] x'_t) * norm_w)``;
+    with ``rows`` (int32) ``h[r]`` is made from row ``rows[r]`` (``x_out`` must then be left out)."""
+    _need(x_in, "streams", torch.float32)
+    if x_in.dim() == 3:
+        n, s_in, width = x_in.shape
+    elif x_in.dim() == 2:
+        (n, width), s_in = x_in.shape, 1
+    else:
+        raise KernelError(f"hc_step: streams are [n, S, W] or [n, W], got {tuple(x_in.shape)}")
+    if not 1 <= n_streams <= HC_MAX_STREAMS or s_in not in (1, n_streams):
+        raise KernelError(f"hc_step: {n_streams} streams (1..{HC_MAX_STREAMS}) against an input of {s_in}")
+    if x_out is not None:
+        if rows is not None:
+            raise KernelError("hc_step: gathered rows are not written back")
+        _need(x_out, "x_out", torch.float32, (n, n_streams, width))
+    act = None
+    if y is not None:
+        _need(y, "y", None, (n, width))
+        _need(mix, "mix", torch.float32, (n_streams, n_streams))
+        _need(outw, "outw", torch.float32, (n_streams,))
+        act = y
+    n_rows = n
+    if inw is not None:
+        _need(inw, "inw", torch.float32, (n_streams,))
+        _need(norm_w, "norm weight", torch.float32, (width,))
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+            n_rows = h.shape[0]
+            if rows.numel() < n_rows:
+                raise KernelError("hc_step: fewer row indices than output rows")
+        _need(h, "h", None, (n_rows, width))
+        if act is not None and h.dtype != act.dtype:
+            raise KernelError(f"hc_step: y is {act.dtype}, h is {h.dtype}")
+        act = h
+    elif rows is not None:
+        raise KernelError("hc_step: rows belong to the norm's output")
+    if act is None:
+        raise KernelError("hc_step: nothing to do (neither y nor inw)")
+    _ok(stream_hc_lib().dryft_hc_step(_act(act, "activations"), _ptr(x_in), s_in, _ptr(x_out), n_streams, _ptr(y), _ptr(mix), _ptr(outw),
+                                      float(mult), _ptr(inw), _ptr(norm_w), float(eps), _ptr(rows), _ptr(h), n_rows, width, _stream()),
+        f"hc_step ({n_streams} streams, width {width})")
+
+
+def glu_clamp(gate_up, out, limit: Optional[float], alpha: float, up_offset: float) -> None:
+    """``out = g * sigmoid(alpha * g) * (u + up_offset)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``
+    (no clamping when ``limit`` is None); ``gate_up [rows, 2F]`` holds the gate columns first."""
+    rows, two_f = gate_up.shape
+    _need(gate_up, "gate_up")
+    if two_f % 2:
+        raise KernelError(f"glu_clamp: fused gate|up width must be even, got {two_f}")
+    _need(out, "glu_clamp output", gate_up.dtype, (rows, two_f // 2))
+    _ok(stream_hc_lib().dryft_glu_clamp(_act(gate_up, "gate_up"), _ptr(gate_up), _ptr(out), rows, two_f // 2,
+                                        float(limit if limit is not None else 0.0), int(limit is not None), float(alpha),
+                                        float(up_offset), _stream()), "glu_clamp")
+
+
+# ----------------------------------------------------------------------------- recurrent mixers
+def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, decay, state, out, n_seqs: int, heads: int,
+                   dim: int, vdim: int, k_scale: float, eps: float) -> None:
+    """Retention over the step's tokens from and to ``state [slots, heads, dim, vdim]`` (float32).  ``proj [n, ld]`` holds
+    q | k | v | g at the column ``offsets`` (4 ints); ``out [n, heads * vdim]``."""
+    n, ld = proj.shape
+    _need(proj, "proj")
+    q_off, k_off, v_off, g_off = (int(o) for o in offsets)
+    if max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim, g_off + heads * vdim) > ld:
+        raise KernelError("retention_scan: column offsets outside the projection row")
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _need(decay, "decay", torch.float32, (heads,))
+    _need(state, "state", torch.float32, (None, heads, dim, vdim))
+    _need(out, "out", proj.dtype, (n, heads * vdim))
+    _ok(recurrent_lib().dryft_retention_scan(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
+                                             _ptr(tok_pos), _ptr(inv_freq), int(rot), _ptr(decay), _ptr(state), _ptr(out), n_seqs,
+                                             heads, dim, vdim, float(k_scale), float(eps), _stream()),
+        f"retention_scan ({heads} heads of {dim} x {vdim})")
+
+
+def rglru(proj, y_off: int, x_off: int, y_bias, x_bias, cu_q, seq_slot, tok_slot, conv_w, conv_b, w_gates, b_a, b_i, sp_lam,
+          c_mult: float, state, tail, out, n_seqs: int, n_blocks: int) -> None:
+    """The gated linear recurrence over ``C`` channels: ``proj [n, ld]`` holds the gelu branch at ``y_off`` and the recurrent
+    branch at ``x_off`` (biases not added yet); ``conv_w [C, taps]``; ``w_gates [blocks, C/blocks (in), 2, C/blocks (out)]``
+    (recurrence gate, input gate); ``state [slots, C]`` and ``tail [slots, taps-1, C]`` float32; ``out [n, C]``.  Two launches."""
+    n, ld = proj.shape
+    c, taps = conv_w.shape
+    _need(proj, "proj")
+    if c % n_blocks or max(y_off, x_off) + c > ld:
+        raise KernelError(f"rglru: {c} channels in {n_blocks} groups, row of {ld}")
+    nb = c // n_blocks
+    for t, nm, shp in ((y_bias, "y_bias", (c,)), (x_bias, "x_bias", (c,)), (conv_w, "conv_w", (c, taps)), (conv_b, "conv_b", (c,)),
+                       (w_gates, "w_gates", (n_blocks, nb, 2, nb)), (b_a, "b_a", (c,)), (b_i, "b_i", (c,)), (sp_lam, "sp_lam", (c,)),
+                       (state, "state", (None, c))):
+        _need(t, nm, torch.float32, shp)
+    if taps > 1:
+        _need(tail, "tail", torch.float32, (state.shape[0], taps - 1, c))
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (tok_slot, "tok_slot")):
+        _need(t, nm, torch.int32)
+    _need(out, "out", proj.dtype, (n, c))
+    a = torch.empty((n, c), dtype=torch.float32, device=proj.device)
+    b = torch.empty((n, c), dtype=torch.float32, device=proj.device)
+    lib = recurrent_lib()
+    is_bf16 = _act(proj, "proj")
+    _ok(lib.dryft_rglru_gates(is_bf16, _ptr(proj), ld, int(x_off), _ptr(x_bias), _ptr(tok_slot), _ptr(conv_w), _ptr(conv_b), taps,
+                              _ptr(tail if taps > 1 else None), _ptr(w_gates), _ptr(b_a), _ptr(b_i), _ptr(sp_lam), float(c_mult),
+                              _ptr(a), _ptr(b), n, c, n_blocks, _stream()), f"rglru_gates ({c} channels, {n_blocks} groups)")
+    _ok(lib.dryft_rglru_scan(is_bf16, _ptr(proj), ld, int(y_off), _ptr(y_bias), int(x_off), _ptr(x_bias), _ptr(cu_q), _ptr(seq_slot),
+                             _ptr(a), _ptr(b), _ptr(state), _ptr(tail if taps > 1 else None), taps, _ptr(out), n_seqs, c, _stream()),
+        f"rglru_scan ({c} channels)")
+
+
+# ----------------------------------------------------------------------------- attention over cached latents
+def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int, rot: int, w_kv, eps: float, inv_freq,
+                interleaved: bool, tok_slot, tok_pos, cq, k_pages, page_table) -> None:
+    """Normalise the query latent into ``cq [n, q_rank]``; normalise the key/value latent, rotate the shared key part and
+    write ``[c | k_rot]`` into the paged cache ``k_pages [pages, 1, page, kv_rank + rot]`` at each token's (slot, position)."""
+    n, ld = proj.shape
+    _need(proj, "proj")
+    if dq_off + q_rank > ld or dkv_off + kv_rank + rot > ld:
+        raise KernelError("latent_prep: column ranges outside the projection row")
+    _need(w_q, "w_q", torch.float32, (q_rank,))
+    _need(w_kv, "w_kv", torch.float32, (kv_rank,))
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _need(tok_slot, "tok_slot", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32)
+    _need(cq, "cq", proj.dtype, (n, q_rank))
+    _need(k_pages, "k_pages", proj.dtype, (None, 1, None, kv_rank + rot))
+    _need(page_table, "page_table", torch.int32)
+    _ok(latent_attn_lib().dryft_latent_prep(_act(proj, "proj"), _ptr(proj), ld, int(dq_off), q_rank, _ptr(w_q), int(dkv_off), kv_rank,
+                                            rot, _ptr(w_kv), float(eps), _ptr(inv_freq), int(interleaved), _ptr(tok_slot),
+                                            _ptr(tok_pos), _ptr(cq), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
+                                            k_pages.shape[2], n, _stream()), "latent_prep")
+
+
+def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, tok_pos, inv_freq, interleaved: bool, o_lat,
+                     kv_rank: int, rot: int, scale: float, window: Optional[int]) -> None:
+    """``o_lat [H, n, kv_rank]``: softmax attention of ``q_lat [H, n, kv_rank]`` (float32, the key matrices folded in) and the
+    rotated part of ``q [n, H, q_stride]`` (at ``q_rot_off``, rotated here) over the cached rows ``[c | k_rot]``."""
+    n_heads, n, _ = q_lat.shape
+    _need(q_lat, "q_lat", torch.float32, (n_heads, n, kv_rank))
+    _need(q, "q", k_pages.dtype, (n, n_heads, None))
+    if q_rot_off + rot > q.shape[2]:
+        raise KernelError("latent_attn_rows: the rotated part lies outside the query rows")
+    _need(k_pages, "k_pages", None, (None, 1, None, kv_rank + rot))
+    for t, nm in ((page_table, "page_table"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _need(o_lat, "o_lat", k_pages.dtype, (n_heads, n, kv_rank))
+    _ok(latent_attn_lib().dryft_latent_attn_rows(_act(k_pages, "k_pages"), _ptr(q_lat), _ptr(q), q.shape[2], int(q_rot_off), _ptr(k_pages),
+                                                 _ptr(page_table), page_table.shape[1], k_pages.shape[2], _ptr(tok_slot), _ptr(tok_pos),
+                                                 _ptr(inv_freq), int(interleaved), _ptr(o_lat), n, n_heads, kv_rank, rot, float(scale),
+                                                 int(window or 0), _stream()), f"latent_attn_rows (rank {kv_rank}, rotated {rot})")
+
+
+def head_gate(o, gate, gate_col: int, out) -> None:
+    """``out[n, h*V + v] = T(o[h, n, v] * sigmoid(gate[n, gate_col + h]))`` (``gate`` None: no gate); ``o`` float32."""
+    n_heads, n, vdim = o.shape
+    _need(o, "o", torch.float32)
+    _need(out, "out", None, (n, n_heads * vdim))
+    gate_ptr, gate_ld = None, 0
+    if gate is not None:
+        _need(gate, "gate", out.dtype)
+        if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+            raise KernelError("head_gate: gate columns outside the gate tensor")
+        gate_ptr, gate_ld = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    _ok(latent_attn_lib().dryft_head_gate(_act(out, "out"), _ptr(o), gate_ptr, gate_ld, _ptr(out), n, n_heads, vdim, _stream()),
+        "head_gate")
+
+
+def gemm_nt_f32_view(a, w, out) -> None:
+    """``gemm_nt_f32`` for 2-D views: ``a [M, K]`` and ``out [M, N]`` may be column ranges of wider rows (unit stride along
+    a row); ``w [N, K]`` is contiguous."""
+    m, k = a.shape
+    n = w.shape[0]
+    for t, nm in ((a, "a"), (out, "out")):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_nt_f32_view: {nm} must be a float32 CUDA matrix with unit stride along rows")
+    _need(w, "w", torch.float32, (n, k))
+    if out.shape != (m, n):
+        raise KernelError(f"gemm_nt_f32_view: out is {tuple(out.shape)}, expected {(m, n)}")
+    _ok(core().dryft_gemm_nt_f32(_ptr(a), a.stride(0), _ptr(w), _ptr(out), out.stride(0), m, n, k, _stream()), "gemm_nt_f32")

@@ -4,12 +4,14 @@ kinds; ``register_*`` adds others without touching any file here."""
 
 from .base import (
     BLOCKS, EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, POSITIONS, Registry, Residual, Runtime, StepContext, TensorInfo,
-    register_block, register_embedding, register_ffn, register_head, register_mixer, register_norm, register_position,
+    CONNECTIONS, register_block, register_connection, register_embedding, register_ffn, register_head, register_mixer,
+    register_norm, register_position,
 )
-from . import attention, block, diff_attention, embedding, ffn, moe, norm, position  # noqa: F401  (registration)
+from . import attention, block, diff_attention, embedding, ffn, hyper, latent_attention, moe, norm, position, retention, rglru  # noqa: F401  (registration)
 from .linear import linear
 
 __all__ = [
+    "CONNECTIONS", "register_connection",
     "BLOCKS", "EMBEDDINGS", "FFNS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "Registry", "Residual", "Runtime", "StepContext",
     "TensorInfo", "linear", "register_block", "register_embedding", "register_ffn", "register_head", "register_mixer",
     "register_norm", "register_position",

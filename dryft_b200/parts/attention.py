@@ -73,6 +73,8 @@ class Attention:
             self.k_norm_w = weights.load(prefix + "k_norm.weight", "vector")
         pos: PartSpec = params.get("position") or PartSpec("none")
         self.position = POSITIONS.get(pos.kind)(pos.params, self.head_dim, rt)
+        if getattr(self.position, "interleaved", False):
+            raise ValueError("attention: this mixer's kernels rotate dims j and j + R/2 together; an interleaved layout is not served")
         # build (or find) the kernels this head shape needs now, not at the first step
         K.attention_rows_lib(self.head_dim, self.group, rt.page_size)
         self.use_prefill_kernel = rt.is_bf16

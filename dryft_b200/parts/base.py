@@ -105,6 +105,10 @@ class Residual:
     # a stream kept in 32-bit whatever the activation type (``x`` is float32): ``h`` is ``x`` rounded to the activation
     # type, what the next sublayer reads (``x`` itself in the 32-bit path)
     h: Optional[torch.Tensor] = None
+    # who adds ``delta`` when it is not a plain sum: the connection (``parts/hyper.py``) whose weights join ``delta`` to
+    # the streams, and the block that turns the streams into the rows the last norm and the head read
+    conn: Optional[Any] = None
+    closer: Optional[Any] = None
 
 
 def fused_rms(norm) -> Optional[Tuple[torch.Tensor, float]]:
@@ -159,7 +163,10 @@ BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
 
-FAMILIES = {"mixer": MIXERS, "ffn": FFNS, "norm": NORMS}   # the registries a layer's extra parts are built from
+CONNECTIONS = Registry("residual connection")
+
+# the registries a layer's extra parts are built from
+FAMILIES = {"mixer": MIXERS, "ffn": FFNS, "norm": NORMS, "connection": CONNECTIONS}
 
 register_mixer = MIXERS.register
 register_ffn = FFNS.register
@@ -168,3 +175,4 @@ register_position = POSITIONS.register
 register_block = BLOCKS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_connection = CONNECTIONS.register

@@ -120,3 +120,63 @@ class LMHead:
         else:
             K.fused_product(x, self.weight, out, small_m_max=small, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         return out
+
+
+@register_embedding("pair_embedding")
+class PairEmbedding:
+    """``x = norm(table[id] * scale + pairs[row]) * w``: the token's row times a constant, plus a row of a second table chosen
+    by a hash of the token and the one before it in its sequence, ``row = (prev * mul_prev + id * mul_cur) mod buckets``; a
+    sequence's first token takes the row behind the buckets (row ``buckets`` of a table of ``buckets + 1`` rows).  The token
+    before the first one of a step is per-sequence state (``state_need``): one int32 per slot, stored after every step.
+    The sum and the norm are 32-bit, and the result starts a 32-bit residual stream (a ``Residual`` whose ``x`` is float32).
+    ``params``: ``scale``; ``pair`` (None, or ``buckets``, ``mul_prev``, ``mul_cur``, ``name``); ``norm`` (None, or ``eps``,
+    ``name``); ``name`` (the table's tensor name behind the prefix)."""
+
+    takes_state = True   # forward needs the step's context and the per-sequence state
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        w = params["hidden_size"]
+        t = {prefix + params.get("name", "weight"): TensorInfo((params["vocab_size"], w), "table")}
+        pair = params.get("pair")
+        if pair:
+            t[prefix + pair.get("name", "pairs")] = TensorInfo((int(pair["buckets"]) + 1, w), "table")
+        norm = params.get("norm")
+        if norm:
+            t[prefix + norm.get("name", "norm.weight")] = TensorInfo((w,), "vector")
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
+        self.table = weights.load(prefix + params.get("name", "weight"), "table")
+        pair = params.get("pair")
+        self.pairs = None
+        self.buckets = self.mul_prev = self.mul_cur = 0
+        if pair:
+            self.buckets, self.mul_prev, self.mul_cur = int(pair["buckets"]), int(pair["mul_prev"]), int(pair["mul_cur"])
+            self.pairs = weights.load(prefix + pair.get("name", "pairs"), "table")
+            if self.pairs.dtype != self.table.dtype:
+                self.pairs = self.pairs.to(self.table.dtype)
+        norm = params.get("norm")
+        self.norm_w, self.eps = None, 0.0
+        if norm:
+            self.norm_w, self.eps = weights.load(prefix + norm.get("name", "norm.weight"), "vector"), float(norm["eps"])
+        self.err = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        K.watch_flag(self.err, "a token id outside the embedding table reached the embedding gather (its row was zeroed)")
+
+    def state_need(self):
+        from ..cache.store import StateNeed
+
+        return StateNeed((), torch.int32) if self.pairs is not None else None
+
+    def forward(self, tokens: torch.Tensor, n_rows: int, ctx: StepContext, state: Optional[torch.Tensor]) -> Residual:
+        x = torch.empty((n_rows, self.hidden), dtype=torch.float32, device=self.table.device)
+        K.embed_pair_norm(tokens, ctx.tok_slot, ctx.tok_pos, self.table, x, scale=self.scale, pair_table=self.pairs,
+                          buckets=self.buckets, mul_prev=self.mul_prev, mul_cur=self.mul_cur, prev_state=state,
+                          norm_w=self.norm_w, eps=self.eps, err=self.err)
+        if self.pairs is not None:
+            K.seq_last_token(tokens, ctx.tok_slot, n_rows, state)
+        return Residual(x)

@@ -81,3 +81,48 @@ class SwiGLU:
         for r0 in range(0, n, chunk):
             out[r0:r0 + chunk] = self._rows(h[r0:r0 + chunk])
         return out
+
+
+@register_ffn("clamped_glu")
+class ClampedGLU:
+    """``down(g * sigmoid(alpha * g) * (u + up_offset))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit,
+    limit)``; gate and up are one product ``[rows, 2I]`` (gate columns first).  ``limit`` None: nothing is clamped.
+    ``params["names"]`` maps ``gate``, ``up``, ``down`` to the tensors' names behind the prefix."""
+
+    @staticmethod
+    def _names(params: Mapping, prefix: str) -> Dict[str, str]:
+        given = params.get("names") or {}
+        return {r: prefix + given.get(r, r + "_proj.weight") for r in ("gate", "up", "down")}
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        h, i = params["hidden_size"], params["intermediate_size"]
+        nm = ClampedGLU._names(params, prefix)
+        return {nm["gate"]: TensorInfo((i, h), "matrix"), nm["up"]: TensorInfo((i, h), "matrix"), nm["down"]: TensorInfo((h, i), "matrix")}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.limit = None if params.get("limit") is None else float(params["limit"])
+        self.alpha = float(params.get("alpha", 1.0))
+        self.up_offset = float(params.get("up_offset", 0.0))
+        nm = self._names(params, prefix)
+        self.w_gate_up = weights.load_fused([nm["gate"], nm["up"]], [self.inter, self.inter], self.hidden)
+        self.w_down = weights.load(nm["down"], "matrix")
+
+    def _rows(self, h: torch.Tensor) -> torch.Tensor:
+        gu = linear(h, self.w_gate_up, self.rt)
+        act = torch.empty((h.shape[0], self.inter), dtype=h.dtype, device=h.device)
+        K.glu_clamp(gu, act, self.limit, self.alpha, self.up_offset)
+        return linear(act, self.w_down, self.rt)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = h.shape[0]
+        chunk = self.rt.ffn_chunk_rows
+        if n <= chunk:
+            return self._rows(h)
+        out = torch.empty((n, self.hidden), dtype=h.dtype, device=h.device)
+        for r0 in range(0, n, chunk):
+            out[r0:r0 + chunk] = self._rows(h[r0:r0 + chunk])
+        return out

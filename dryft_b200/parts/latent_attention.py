@@ -1,0 +1,128 @@
+"""Attention whose queries, keys and values come from low-rank latents, over a sliding window, with a gate per head.
+
+With ``H`` heads, per head ``d`` unrotated and ``r`` rotated query/key dims, value size ``dv``, latent sizes ``q_rank`` and
+``kv_rank``, and ``h`` the mixer's input:
+
+    c_q = rmsnorm(W_dq h) ;  q = W_uq c_q            (head by head: ``d`` unrotated dims, then ``r`` rotated ones)
+    [c_raw | k_rot] = W_dkv h ;  c = rmsnorm(c_raw) ;  k_rot rotated at the token's position, one vector for all heads
+    per head:  k = W_uk c ,  v = W_uv c ;  score(i, j) = (q_plain . k + q_rot . k_rot) * scale ,  0 <= i - j < window
+    o = softmax(score) v ;  o <- o * sigmoid(W_g h)_head  ->  @ W_o.T
+
+Only ``[c | k_rot]`` is cached, one row per token for all heads (a keys-only cache group).  The per-head key and value
+matrices are folded into the query and the output: ``q_lat = W_uk^T q_plain`` before attention, ``o = W_uv o_lat`` after,
+both as batched matrix products over the heads; attention itself runs over the cached rows (``csrc/latent_attn.cu``).
+Norms, angles, scores, softmax and the weighted sum are 32-bit in both precisions.  ``W_dq | W_dkv | W_g`` are one
+product.  Every size and constant is a parameter; ``params["names"]`` maps the tensors' roles to their names.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.store import CacheEntry, KVNeed, StateNeed
+from ..config.spec import PartSpec
+from ..ops import kernels as K
+from .base import POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
+from .linear import linear
+
+_ROLES = {"dq": "q_down.weight", "dq_norm": "q_down.norm", "uq": "q_up.weight", "dkv": "kv_down.weight", "dkv_norm": "kv_down.norm",
+          "uk": "k_up.weight", "uv": "v_up.weight", "gate": "g_proj.weight", "o": "o_proj.weight"}
+
+
+def _names(params: Mapping, prefix: str) -> Dict[str, str]:
+    given = params.get("names") or {}
+    return {role: prefix + given.get(role, default) for role, default in _ROLES.items()}
+
+
+@register_mixer("latent_attention")
+class LatentAttention:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        w, h, d, r, dv = params["hidden_size"], params["num_heads"], params["qk_dim"], params["rot_dim"], params["v_dim"]
+        qr, kr = params["q_rank"], params["kv_rank"]
+        nm = _names(params, prefix)
+        t = {nm["dq"]: TensorInfo((qr, w), "matrix"), nm["dq_norm"]: TensorInfo((qr,), "vector"),
+             nm["uq"]: TensorInfo((h * (d + r), qr), "matrix"), nm["dkv"]: TensorInfo((kr + r, w), "matrix"),
+             nm["dkv_norm"]: TensorInfo((kr,), "vector"), nm["uk"]: TensorInfo((h * d, kr), "matrix"),
+             nm["uv"]: TensorInfo((h * dv, kr), "matrix"), nm["o"]: TensorInfo((w, h * dv), "matrix")}
+        if params.get("gate", True):
+            t[nm["gate"]] = TensorInfo((h, w), "matrix")
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.n_heads = int(params["num_heads"])
+        self.qk_dim = int(params["qk_dim"])
+        self.rot_dim = int(params["rot_dim"])
+        self.v_dim = int(params["v_dim"])
+        self.q_rank = int(params["q_rank"])
+        self.kv_rank = int(params["kv_rank"])
+        self.scale = float(params["scale"])
+        self.eps = float(params["eps"])
+        self.window: Optional[int] = params.get("window")
+        self.has_gate = bool(params.get("gate", True))
+        if self.kv_rank > 512:
+            raise ValueError(f"latent_attention: latents of up to 512 are served, got kv_rank={self.kv_rank}")
+        pos: PartSpec = params.get("position") or PartSpec("none")
+        self.position = POSITIONS.get(pos.kind)(pos.params, max(self.rot_dim, 2), rt) if self.rot_dim else POSITIONS.get("none")({}, 0, rt)
+        if self.position.rotary_dim not in (0, self.rot_dim):
+            raise ValueError(f"latent_attention: the rotation covers the whole rotated part ({self.rot_dim} dims), got {self.position.rotary_dim}")
+        nm = _names(params, prefix)
+        names, rows = [nm["dq"], nm["dkv"]], [self.q_rank, self.kv_rank + self.rot_dim]
+        if self.has_gate:
+            names.append(nm["gate"])
+            rows.append(self.n_heads)
+        self.w_in = weights.load_fused(names, rows, self.hidden)    # one product for everything that reads the mixer's input
+        self.dkv_off = self.q_rank
+        self.gate_col = self.q_rank + self.kv_rank + self.rot_dim
+        self.w_uq = weights.load(nm["uq"], "matrix")
+        self.w_o = weights.load(nm["o"], "matrix")
+        self.dq_norm_w = weights.load(nm["dq_norm"], "vector")
+        self.dkv_norm_w = weights.load(nm["dkv_norm"], "vector")
+        H, d, dv, kr = self.n_heads, self.qk_dim, self.v_dim, self.kv_rank
+        w_uk = weights.load(nm["uk"], "matrix")      # [H*d, kr]
+        w_uv = weights.load(nm["uv"], "matrix")      # [H*dv, kr]
+        # per head: q_lat = q_plain @ W_uk,h ([d, kr]) and o = o_lat @ W_uv,h^T ([kr, dv])
+        self.w_uk = w_uk.reshape(H, d, kr).contiguous()
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()        # [H, kr, d]: rows = outputs, for the 32-bit product
+        self.w_uv = w_uv.reshape(H, dv, kr).contiguous()            # [H, dv, kr]: rows = outputs
+        K.latent_attn_lib()
+
+    def kv_need(self) -> KVNeed:
+        return KVNeed(1, self.kv_rank + self.rot_dim, self.window, values=False)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("latent_attention: every layer writes its own latents")
+        n, dev, H = h.shape[0], h.device, self.n_heads
+        d, r, dv, kr = self.qk_dim, self.rot_dim, self.v_dim, self.kv_rank
+        proj = linear(h, self.w_in, self.rt)
+        cq = torch.empty((n, self.q_rank), dtype=h.dtype, device=dev)
+        K.latent_prep(proj, 0, self.q_rank, self.dq_norm_w, self.dkv_off, kr, r, self.dkv_norm_w, self.eps, self.position.inv_freq,
+                      self.position.interleaved, ctx.tok_slot, ctx.tok_pos, cq, cache.k, cache.page_table)
+        q = linear(cq, self.w_uq, self.rt).view(n, H, d + r)
+        q_lat = self._per_head(q[:, :, :d].transpose(0, 1), self.w_uk, self.w_uk_t)
+        o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
+        K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
+                           self.position.interleaved, o_lat, kr, r, self.scale, self.window)
+        o = self._per_head(o_lat, self.w_uv.transpose(1, 2), self.w_uv)
+        out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
+        K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)
+        return linear(out, self.w_o, self.rt)
+
+    def _per_head(self, a: torch.Tensor, w_kn: torch.Tensor, w_nk: torch.Tensor) -> torch.Tensor:
+        """``a[h] @ w[h]`` for every head, as float32 ``[H, n, m]``.  ``a [H, n, k]`` (any strides with unit stride along k),
+        ``w_kn [H, k, m]`` / ``w_nk [H, m, k]`` the same matrices in both layouts.  bfloat16: one batched library product
+        (32-bit accumulation); 32-bit: the CUDA-core product head by head."""
+        if a.dtype == torch.float32:
+            out = torch.empty((a.shape[0], a.shape[1], w_nk.shape[1]), dtype=torch.float32, device=a.device)
+            for hd in range(a.shape[0]):
+                K.gemm_nt_f32_view(a[hd], w_nk[hd], out[hd])
+            return out
+        return torch.bmm(a, w_kn, out_dtype=torch.float32)

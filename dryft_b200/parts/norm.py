@@ -16,15 +16,17 @@ from .base import Runtime, TensorInfo, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm:
+    """``params["name"]`` is the weight's tensor name behind the prefix (default ``weight``)."""
+
     @staticmethod
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
-        return {prefix + "weight": TensorInfo((params["size"],), "vector")}
+        return {prefix + params.get("name", "weight"): TensorInfo((params["size"],), "vector")}
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.rt = rt
-        self.weight = weights.load(prefix + "weight", "vector")  # float32 [size]
+        self.weight = weights.load(prefix + params.get("name", "weight"), "vector")  # float32 [size]
 
     def rms_params(self):
         """This norm is ``weight * cast(x32 * rsqrt(mean(x32^2) + eps))``: products may fold it into themselves."""

@@ -27,13 +27,26 @@ TABLE_MIN_TOKENS = 64   # below this every warp evaluates its own angles
 
 @register_position("rope")
 class Rope:
+    """``params["layout"]``: ``"half"`` (dims ``j`` and ``j + R/2`` turn together; the default) or ``"interleaved"`` (dims
+    ``2j`` and ``2j + 1``); the mixers whose kernels take both read ``interleaved``.  ``params["freq"]``: ``"float32"``
+    (the reference's expression, evaluated in 32-bit; the default) or ``"rounded_once"`` (``theta^(-2j/R)`` evaluated in
+    64-bit and rounded to 32-bit once)."""
+
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = int(params.get("rotary_dim", head_dim))
         self.theta = float(params["theta"])
         if self.rotary_dim <= 0 or self.rotary_dim % 2 or self.rotary_dim > head_dim:
             raise ValueError(f"rope: rotary_dim must be even and in (0, head_dim={head_dim}], got {self.rotary_dim}")
+        layout = params.get("layout", "half")
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"rope: layout must be 'half' or 'interleaved', got {layout!r}")
+        self.interleaved = layout == "interleaved"
         r = self.rotary_dim
-        inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
+        if params.get("freq", "float32") == "rounded_once":
+            inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
+                                 -torch.arange(0, r, 2, dtype=torch.float64) / r).to(torch.float32)
+        else:
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
         self.inv_freq: Optional[torch.Tensor] = inv_freq.to(rt.device)
         self.dtype = rt.dtype
 
@@ -54,6 +67,7 @@ class NoPosition:
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = 0
         self.inv_freq = None
+        self.interleaved = False
 
     def table(self, ctx: StepContext) -> None:
         return None
