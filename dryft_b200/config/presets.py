@@ -93,6 +93,41 @@ PRESETS.update({
 EQUAL_SIZE = {"tevovik-1k": "qwen3-1k", "tevovik-2k": "qwen3-2k"}   # a Tevovik shape -> the dense shape of equal size
 
 
+def _vobusun(width: int, heads: int, head_dim: int, ff: int, vocab: int, repeats: int, window: int, q_rank: int, kv_rank: int,
+             rot_dim: int, rec_blocks: int, streams: int = 4) -> dict:
+    """A Vobusun ``config.json``: a group of four layers (gated recurrence, two retention layers, latent attention) run
+    ``repeats`` times, every run after the first with the first group's weights and a state of its own."""
+    decay = [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, heads - 1)) for h in range(heads)]
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    ret = {"type": "retention", "mlp": mlp,
+           "mixer": {"heads": heads, "dim": head_dim, "vdim": head_dim, "decay": decay, "rot": {"dims": head_dim, "base": 1000000.0}}}
+    group = [
+        {"type": "rglru", "mixer": {"width": width, "conv": 4, "blocks": rec_blocks}, "mlp": mlp},
+        ret, ret,
+        {"type": "latent_attention", "mlp": mlp,
+         "mixer": {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank,
+                   "scale": (head_dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 10000.0}, "mask": {"size": window}}},
+    ]
+    layers = [dict(l) for l in group]
+    for _ in range(repeats - 1):
+        layers += [dict(l, weights_of=j) for j, l in enumerate(group)]
+    return {"architecture": "Vobusun", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 1009, "mul_cur": 31}},
+            "norm": {"eps": 1e-6}, "residual_mult": 0.7, "streams": streams, "layers": layers}
+
+
+# Vobusun shapes with layers the size of a real model's, and beside each the dense Qwen3 shape of equal size (the same width,
+# layer count, head count, head size, intermediate size and vocabulary).
+PRESETS.update({
+    "vobusun-tiny": _vobusun(width=64, heads=2, head_dim=16, ff=96, vocab=256, repeats=2, window=48, q_rank=24, kv_rank=32,
+                             rot_dim=8, rec_blocks=4, streams=2),
+    "vobusun-1k": _vobusun(width=1024, heads=8, head_dim=128, ff=2048, vocab=32768, repeats=2, window=1024, q_rank=384,
+                           kv_rank=256, rot_dim=64, rec_blocks=8),
+    "vobusun-2k": _vobusun(width=2048, heads=16, head_dim=128, ff=6144, vocab=65536, repeats=3, window=1024, q_rank=768,
+                           kv_rank=512, rot_dim=64, rec_blocks=16),
+})
+EQUAL_SIZE.update({"vobusun-1k": "qwen3-1k", "vobusun-2k": "qwen3-2k"})
+
+
 def preset(name: str) -> dict:
     if name not in PRESETS:
         raise KeyError(f"unknown preset {name!r}; known: " + ", ".join(sorted(PRESETS)))

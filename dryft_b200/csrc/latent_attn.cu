@@ -16,7 +16,7 @@
 //                    o_lat [H, N, kv_rank].
 // head_gate          out[n, h, :] = T( o[h, n, :] * sigmoid(gate_logit[n, h]) )
 //
-// Rotation: pairs (2i, 2i+1) when `interleaved`, else (i, i + R/2); angle = position * inv_freq[i] in 32-bit.
+// Rotation: pairs (2i, 2i+1) when `interleaved`, else (i, i + R/2); angle = position * inv_freq[i] (sincos_split below).
 // Norms, angles, scores, softmax and the weighted sum are 32-bit whatever the cache type T.  Sizes are runtime arguments
 // (kv_rank up to 512).  No block waits on another.
 #include "common.cuh"
@@ -27,22 +27,38 @@ constexpr int PREP_THREADS = 256;
 constexpr int HPB = 4;         // heads (warps) per block of latent_attn_rows
 constexpr int KT = 32;         // keys per staged tile
 
-__device__ __forceinline__ float rotated(const float* v, int d, int R, bool interleaved, float pos, const float* inv_freq) {
+// sin and cos of  pos * (f_hi + f_lo)  for a rotary position: the product is formed in 32-bit, and what its rounding
+// drops (recovered exactly with one fused multiply-add) plus the low half of the frequency are applied as a first-order
+// turn, so the angle is as good as the frequency pair instead of losing one part in 2^24 of a large angle.  f_lo = 0 gives
+// the plain 32-bit angle to within that correction.
+__device__ __forceinline__ void sincos_split(float pos, float f_hi, float f_lo, float* sn, float* cs) {
+  const float a = pos * f_hi;
+  const float e = fmaf(pos, f_hi, -a) + pos * f_lo;
+  float s, c;
+  sincosf(a, &s, &c);
+  *sn = fmaf(e, c, s);
+  *cs = fmaf(-e, s, c);
+}
+
+
+__device__ __forceinline__ float rotated(const float* v, int d, int R, bool interleaved, float pos, const float* inv_freq,
+                                         const float* inv_freq_lo) {
   // entry d (< R) of v after the rotation
   int j, partner;
   bool first;
   if (interleaved) { j = d >> 1; first = !(d & 1); partner = first ? d + 1 : d - 1; }
   else { const int half = R >> 1; first = d < half; j = first ? d : d - half; partner = first ? d + half : d - half; }
   float sn, cs;
-  sincosf(pos * inv_freq[j], &sn, &cs);
+  sincos_split(pos, inv_freq[j], inv_freq_lo ? inv_freq_lo[j] : 0.f, &sn, &cs);
   return first ? v[d] * cs - v[partner] * sn : v[d] * cs + v[partner] * sn;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
     const T* __restrict__ proj, int ld, int dq_off, int q_rank, const float* __restrict__ w_q, int dkv_off, int kv_rank,
-    int rot, const float* __restrict__ w_kv, float eps, const float* __restrict__ inv_freq, int interleaved,
-    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, T* __restrict__ cq, T* __restrict__ k_pages,
+    int rot, const float* __restrict__ w_kv, float eps, const float* __restrict__ inv_freq,
+    const float* __restrict__ inv_freq_lo, int interleaved, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, T* __restrict__ cq, T* __restrict__ k_pages,
     const int* __restrict__ page_table, int max_pages, int page_size) {
   extern __shared__ __align__(16) float buf[];   // [rot]
   __shared__ float scratch[33];
@@ -68,15 +84,15 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
   const float inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
   for (int c = threadIdx.x; c < kv_rank; c += PREP_THREADS) dst[c] = from_f32<T>(to_f32<T>(row[dkv_off + c]) * inv * w_kv[c]);
   for (int c = threadIdx.x; c < rot; c += PREP_THREADS)
-    dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq));
+    dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
 }
 
 template <typename T, int NR>
 __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
     const float* __restrict__ q_lat, const T* __restrict__ q, int q_stride, int q_rot_off, const T* __restrict__ k_pages,
     const int* __restrict__ page_table, int max_pages, int page_size, const int* __restrict__ tok_slot,
-    const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int interleaved, T* __restrict__ o_lat, int n_tokens,
-    int H, int kv_rank, int rot, float scale, int window) {
+    const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
+    int interleaved, T* __restrict__ o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window) {
   extern __shared__ __align__(16) float sm[];
   const int Dk = kv_rank + rot, Dp = Dk + 1;
   float* tile = sm;                                  // [KT][Dp]
@@ -98,7 +114,7 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
     float* rw = raw + (size_t)warp * rot;
     for (int d = lane; d < rot; d += 32) rw[d] = to_f32<T>(qr[d]);
     __syncwarp();
-    for (int d = lane; d < rot; d += 32) qs[kv_rank + d] = rotated(rw, d, rot, interleaved != 0, (float)pos, inv_freq) * scale;
+    for (int d = lane; d < rot; d += 32) qs[kv_rank + d] = rotated(rw, d, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo) * scale;
   }
   float m = -INFINITY, l = 0.f;
   float acc[NR];
@@ -176,23 +192,23 @@ template <typename K> int opt_in(K kernel, size_t bytes) {
 
 template <typename T, int NR>
 int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, const void* k_pages, const int* page_table,
-                int max_pages, int page_size, const int* tok_slot, const int* tok_pos, const float* inv_freq, int interleaved,
-                void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+                int max_pages, int page_size, const int* tok_slot, const int* tok_pos, const float* inv_freq,
+                const float* inv_freq_lo, int interleaved, void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
   const int Dk = kv_rank + rot;
   const size_t smem = sizeof(float) * ((size_t)KT * (Dk + 1) + (size_t)HPB * Dk + (size_t)HPB * rot);
   int rc = opt_in(latent_attn_rows_kernel<T, NR>, smem);
   if (rc) return rc;
   dim3 grid(n_tokens, (H + HPB - 1) / HPB);
   latent_attn_rows_kernel<T, NR><<<grid, HPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
-                                                               max_pages, page_size, tok_slot, tok_pos, inv_freq, interleaved,
-                                                               (T*)o_lat, n_tokens, H, kv_rank, rot, scale, window);
+                                                               max_pages, page_size, tok_slot, tok_pos, inv_freq, inv_freq_lo,
+                                                               interleaved, (T*)o_lat, n_tokens, H, kv_rank, rot, scale, window);
   return launch_status();
 }
 }  // namespace
 
 DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_off, int q_rank, const float* w_q, int dkv_off,
-                                int kv_rank, int rot, const float* w_kv, float eps, const float* inv_freq, int interleaved,
-                                const int* tok_slot, const int* tok_pos, void* cq, void* k_pages, const int* page_table,
+                                int kv_rank, int rot, const float* w_kv, float eps, const float* inv_freq,
+                                const float* inv_freq_lo, int interleaved, const int* tok_slot, const int* tok_pos, void* cq, void* k_pages, const int* page_table,
                                 int max_pages, int page_size, int n, cudaStream_t st) {
   if (n <= 0) return 0;
   if (kv_rank <= 0 || rot < 0 || (rot & 1)) return DRYFT_ERR_UNSUPPORTED;
@@ -201,28 +217,28 @@ DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_of
   if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (is_bf16)
     latent_prep_kernel<bf><<<n, PREP_THREADS, smem, st>>>((const bf*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv, eps,
-                                                          inv_freq, interleaved, tok_slot, tok_pos, (bf*)cq, (bf*)k_pages, page_table,
+                                                          inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos, (bf*)cq, (bf*)k_pages, page_table,
                                                           max_pages, page_size);
   else
     latent_prep_kernel<float><<<n, PREP_THREADS, smem, st>>>((const float*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv,
-                                                             eps, inv_freq, interleaved, tok_slot, tok_pos, (float*)cq, (float*)k_pages,
+                                                             eps, inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos, (float*)cq, (float*)k_pages,
                                                              page_table, max_pages, page_size);
   return launch_status();
 }
 
 DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void* q, int q_stride, int q_rot_off,
                                      const void* k_pages, const int* page_table, int max_pages, int page_size,
-                                     const int* tok_slot, const int* tok_pos, const float* inv_freq, int interleaved, void* o_lat,
-                                     int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+                                     const int* tok_slot, const int* tok_pos, const float* inv_freq, const float* inv_freq_lo,
+                                     int interleaved, void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (kv_rank <= 0 || kv_rank > 512 || rot < 0 || (rot & 1) || H <= 0 || (H + HPB - 1) / HPB > 65535) return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
   const int nr = (kv_rank + 31) / 32;
 #define DRYFT_LATENT_ROWS(NR)                                                                                                      \
   return is_bf16 ? launch_rows<bf, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot, tok_pos,  \
-                                       inv_freq, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)                \
+                                       inv_freq, inv_freq_lo, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)                \
                  : launch_rows<float, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot,      \
-                                          tok_pos, inv_freq, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)
+                                          tok_pos, inv_freq, inv_freq_lo, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)
   if (nr <= 1) { DRYFT_LATENT_ROWS(1); }
   if (nr <= 2) { DRYFT_LATENT_ROWS(2); }
   if (nr <= 4) { DRYFT_LATENT_ROWS(4); }

@@ -7,7 +7,7 @@
 //                        o_t = S_t^T q_t ;  o_t <- o_t / sqrt(mean(o_t^2) + eps) ;  out = T( o_t * silu(g_t) )
 //                    One block per (sequence, head) walks the sequence's tokens in order with S in shared memory.
 //                    q | k | v | g are columns of one projection row (offsets given); the rotation pairs entry i with
-//                    entry i + R/2 of the first R entries (angle = position * inv_freq[i], 32-bit).
+//                    entry i + R/2 of the first R entries (angle = position * inv_freq[i]; see sincos_split below).
 //
 // rglru_gates        the input side of a real-gated linear recurrent unit over C channels in `blocks` equal groups:
 //                        x_t  = xproj_t + x_bias                                   (a column range of the projection row)
@@ -28,11 +28,25 @@
 namespace {
 constexpr int RT_THREADS = 256;
 
+// sin and cos of  pos * (f_hi + f_lo)  for a rotary position: the product is formed in 32-bit, and what its rounding
+// drops (recovered exactly with one fused multiply-add) plus the low half of the frequency are applied as a first-order
+// turn, so the angle is as good as the frequency pair instead of losing one part in 2^24 of a large angle.  f_lo = 0 gives
+// the plain 32-bit angle to within that correction.
+__device__ __forceinline__ void sincos_split(float pos, float f_hi, float f_lo, float* sn, float* cs) {
+  const float a = pos * f_hi;
+  const float e = fmaf(pos, f_hi, -a) + pos * f_lo;
+  float s, c;
+  sincosf(a, &s, &c);
+  *sn = fmaf(e, c, s);
+  *cs = fmaf(-e, s, c);
+}
+
+
 template <typename T>
 __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
     const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int g_off, const int* __restrict__ cu_q,
-    const int* __restrict__ seq_slot, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int rot,
-    const float* __restrict__ decay, float* __restrict__ state, T* __restrict__ out, int H, int dim, int vdim,
+    const int* __restrict__ seq_slot, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
+    const float* __restrict__ inv_freq_lo, int rot, const float* __restrict__ decay, float* __restrict__ state, T* __restrict__ out, int H, int dim, int vdim,
     float k_scale, float eps) {
   extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.x, hd = blockIdx.y;
@@ -67,7 +81,7 @@ __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
         const int j = d < half ? d : d - half;
         const float other = to_f32<T>(src[d < half ? d + half : d - half]);
         float sn, cs;
-        sincosf(pos * inv_freq[j], &sn, &cs);
+        sincos_split(pos, inv_freq[j], inv_freq_lo ? inv_freq_lo[j] : 0.f, &sn, &cs);
         val = d < half ? val * cs - other * sn : val * cs + other * sn;
       }
       if (is_k) ks[d] = val * k_scale; else qs[d] = val;
@@ -211,8 +225,8 @@ template <typename K> int opt_in_smem(K kernel, size_t bytes) {
 }  // namespace
 
 DRYFT_API int dryft_retention_scan(int is_bf16, const void* proj, int ld, int q_off, int k_off, int v_off, int g_off,
-                                   const int* cu_q, const int* seq_slot, const int* tok_pos, const float* inv_freq, int rot,
-                                   const float* decay, float* state, void* out, int n_seqs, int H, int dim, int vdim,
+                                   const int* cu_q, const int* seq_slot, const int* tok_pos, const float* inv_freq,
+                                   const float* inv_freq_lo, int rot, const float* decay, float* state, void* out, int n_seqs, int H, int dim, int vdim,
                                    float k_scale, float eps, cudaStream_t st) {
   if (n_seqs <= 0) return 0;
   if (H <= 0 || dim <= 0 || vdim <= 0 || rot < 0 || rot > dim || (rot & 1) || H > 65535) return DRYFT_ERR_UNSUPPORTED;
@@ -224,10 +238,10 @@ DRYFT_API int dryft_retention_scan(int is_bf16, const void* proj, int ld, int q_
   dim3 grid(n_seqs, H);
   if (is_bf16)
     retention_scan_kernel<bf><<<grid, RT_THREADS, smem, st>>>((const bf*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot, tok_pos,
-                                                              inv_freq, rot, decay, state, (bf*)out, H, dim, vdim, k_scale, eps);
+                                                              inv_freq, inv_freq_lo, rot, decay, state, (bf*)out, H, dim, vdim, k_scale, eps);
   else
     retention_scan_kernel<float><<<grid, RT_THREADS, smem, st>>>((const float*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot,
-                                                                 tok_pos, inv_freq, rot, decay, state, (float*)out, H, dim, vdim,
+                                                                 tok_pos, inv_freq, inv_freq_lo, rot, decay, state, (float*)out, H, dim, vdim,
                                                                  k_scale, eps);
   return launch_status();
 }

@@ -1218,7 +1218,7 @@ def stream_hc_lib() -> ctypes.CDLL:
 def recurrent_lib() -> ctypes.CDLL:
     """Mixers with a fixed-size 32-bit state per sequence: retention, gated linear recurrence."""
     return _single_lib("recurrent", {
-        "dryft_retention_scan": [_i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p],
+        "dryft_retention_scan": [_i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p],
         "dryft_rglru_gates": [_i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _f, _p, _p, _i, _i, _i, _p],
         "dryft_rglru_scan": [_i, _p, _i, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p],
     })
@@ -1227,8 +1227,8 @@ def recurrent_lib() -> ctypes.CDLL:
 def latent_attn_lib() -> ctypes.CDLL:
     """Attention over cached low-rank latents."""
     return _single_lib("latent_attn", {
-        "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p],
-        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
+        "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
         "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
     })
 
@@ -1330,9 +1330,19 @@ def glu_clamp(gate_up, out, limit: Optional[float], alpha: float, up_offset: flo
 
 
 # ----------------------------------------------------------------------------- recurrent mixers
+def _freq_lo(inv_freq_lo, rot: int):
+    if inv_freq_lo is not None and rot:
+        _need(inv_freq_lo, "inv_freq_lo", torch.float32, (rot // 2,))
+        return inv_freq_lo
+    return None
+
+
 def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, decay, state, out, n_seqs: int, heads: int,
-                   dim: int, vdim: int, k_scale: float, eps: float) -> None:
-    """Retention over the step's tokens from and to ``state [slots, heads, dim, vdim]`` (float32).  ``proj [n, ld]`` holds
+                   dim: int, vdim: int, k_scale: float, eps: float, inv_freq_lo=None) -> None:
+    """``inv_freq_lo`` (optional, here and in the latent attention wrappers): the part of each frequency that its 32-bit
+    value drops; with it the angles are as exact as the pair.
+
+    Retention over the step's tokens from and to ``state [slots, heads, dim, vdim]`` (float32).  ``proj [n, ld]`` holds
     q | k | v | g at the column ``offsets`` (4 ints); ``out [n, heads * vdim]``."""
     n, ld = proj.shape
     _need(proj, "proj")
@@ -1347,7 +1357,7 @@ def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, d
     _need(state, "state", torch.float32, (None, heads, dim, vdim))
     _need(out, "out", proj.dtype, (n, heads * vdim))
     _ok(recurrent_lib().dryft_retention_scan(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
-                                             _ptr(tok_pos), _ptr(inv_freq), int(rot), _ptr(decay), _ptr(state), _ptr(out), n_seqs,
+                                             _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state), _ptr(out), n_seqs,
                                              heads, dim, vdim, float(k_scale), float(eps), _stream()),
         f"retention_scan ({heads} heads of {dim} x {vdim})")
 
@@ -1386,7 +1396,7 @@ def rglru(proj, y_off: int, x_off: int, y_bias, x_bias, cu_q, seq_slot, tok_slot
 
 # ----------------------------------------------------------------------------- attention over cached latents
 def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int, rot: int, w_kv, eps: float, inv_freq,
-                interleaved: bool, tok_slot, tok_pos, cq, k_pages, page_table) -> None:
+                interleaved: bool, tok_slot, tok_pos, cq, k_pages, page_table, inv_freq_lo=None) -> None:
     """Normalise the query latent into ``cq [n, q_rank]``; normalise the key/value latent, rotate the shared key part and
     write ``[c | k_rot]`` into the paged cache ``k_pages [pages, 1, page, kv_rank + rot]`` at each token's (slot, position)."""
     n, ld = proj.shape
@@ -1403,13 +1413,13 @@ def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int,
     _need(k_pages, "k_pages", proj.dtype, (None, 1, None, kv_rank + rot))
     _need(page_table, "page_table", torch.int32)
     _ok(latent_attn_lib().dryft_latent_prep(_act(proj, "proj"), _ptr(proj), ld, int(dq_off), q_rank, _ptr(w_q), int(dkv_off), kv_rank,
-                                            rot, _ptr(w_kv), float(eps), _ptr(inv_freq), int(interleaved), _ptr(tok_slot),
+                                            rot, _ptr(w_kv), float(eps), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(tok_slot),
                                             _ptr(tok_pos), _ptr(cq), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
                                             k_pages.shape[2], n, _stream()), "latent_prep")
 
 
 def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, tok_pos, inv_freq, interleaved: bool, o_lat,
-                     kv_rank: int, rot: int, scale: float, window: Optional[int]) -> None:
+                     kv_rank: int, rot: int, scale: float, window: Optional[int], inv_freq_lo=None) -> None:
     """``o_lat [H, n, kv_rank]``: softmax attention of ``q_lat [H, n, kv_rank]`` (float32, the key matrices folded in) and the
     rotated part of ``q [n, H, q_stride]`` (at ``q_rot_off``, rotated here) over the cached rows ``[c | k_rot]``."""
     n_heads, n, _ = q_lat.shape
@@ -1425,7 +1435,7 @@ def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, to
     _need(o_lat, "o_lat", k_pages.dtype, (n_heads, n, kv_rank))
     _ok(latent_attn_lib().dryft_latent_attn_rows(_act(k_pages, "k_pages"), _ptr(q_lat), _ptr(q), q.shape[2], int(q_rot_off), _ptr(k_pages),
                                                  _ptr(page_table), page_table.shape[1], k_pages.shape[2], _ptr(tok_slot), _ptr(tok_pos),
-                                                 _ptr(inv_freq), int(interleaved), _ptr(o_lat), n, n_heads, kv_rank, rot, float(scale),
+                                                 _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(o_lat), n, n_heads, kv_rank, rot, float(scale),
                                                  int(window or 0), _stream()), f"latent_attn_rows (rank {kv_rank}, rotated {rot})")
 
 

@@ -37,13 +37,15 @@ from ..config.spec import PartSpec
 
 class TensorInfo(NamedTuple):
     """One checkpoint tensor a part expects.  ``kind``: "matrix" (a product's weight), "vector"
-    (norm weights and other 1-D tensors, kept in 32-bit on the device) or "table" (embedding).  ``mean``: what random
-    weights of this tensor are drawn around (default: 1 for vectors, 0 for everything else)."""
+    (norm weights and other small tensors, kept in 32-bit on the device) or "table" (embedding).  ``mean``: what random
+    weights of this tensor are drawn around (default: 1 for vectors, 0 for everything else).  ``eye``: random weights of a
+    square tensor are drawn around ``eye`` times the identity (a mixing matrix that starts near "every stream keeps itself")."""
 
     shape: Tuple[int, ...]
     kind: str
     optional: bool = False
     mean: Optional[float] = None
+    eye: float = 0.0
 
 
 @dataclass

@@ -37,7 +37,7 @@ class HyperConnection:
             return {}
         opt = int(s) == 1
         return {prefix + "in": TensorInfo((s,), "vector", opt), prefix + "out": TensorInfo((s,), "vector", opt),
-                prefix + "mix": TensorInfo((s, s), "vector", opt, 0.0)}
+                prefix + "mix": TensorInfo((s, s), "vector", opt, 0.0, 1.0)}
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
         s = params.get("streams")

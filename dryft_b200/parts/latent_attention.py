@@ -105,12 +105,14 @@ class LatentAttention:
         proj = linear(h, self.w_in, self.rt)
         cq = torch.empty((n, self.q_rank), dtype=h.dtype, device=dev)
         K.latent_prep(proj, 0, self.q_rank, self.dq_norm_w, self.dkv_off, kr, r, self.dkv_norm_w, self.eps, self.position.inv_freq,
-                      self.position.interleaved, ctx.tok_slot, ctx.tok_pos, cq, cache.k, cache.page_table)
+                      self.position.interleaved, ctx.tok_slot, ctx.tok_pos, cq, cache.k, cache.page_table,
+                      inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
         q = linear(cq, self.w_uq, self.rt).view(n, H, d + r)
         q_lat = self._per_head(q[:, :, :d].transpose(0, 1), self.w_uk, self.w_uk_t)
         o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
         K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
-                           self.position.interleaved, o_lat, kr, r, self.scale, self.window)
+                           self.position.interleaved, o_lat, kr, r, self.scale, self.window,
+                           inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
         o = self._per_head(o_lat, self.w_uv.transpose(1, 2), self.w_uv)
         out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
         K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)

@@ -30,7 +30,7 @@ class Rope:
     """``params["layout"]``: ``"half"`` (dims ``j`` and ``j + R/2`` turn together; the default) or ``"interleaved"`` (dims
     ``2j`` and ``2j + 1``); the mixers whose kernels take both read ``interleaved``.  ``params["freq"]``: ``"float32"``
     (the reference's expression, evaluated in 32-bit; the default) or ``"rounded_once"`` (``theta^(-2j/R)`` evaluated in
-    64-bit and rounded to 32-bit once)."""
+    64-bit and rounded to 32-bit once; what that rounding drops is kept as ``inv_freq_lo`` for kernels that take the pair)."""
 
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = int(params.get("rotary_dim", head_dim))
@@ -42,9 +42,11 @@ class Rope:
             raise ValueError(f"rope: layout must be 'half' or 'interleaved', got {layout!r}")
         self.interleaved = layout == "interleaved"
         r = self.rotary_dim
+        self.inv_freq_lo: Optional[torch.Tensor] = None
         if params.get("freq", "float32") == "rounded_once":
-            inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
-                                 -torch.arange(0, r, 2, dtype=torch.float64) / r).to(torch.float32)
+            exact = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -torch.arange(0, r, 2, dtype=torch.float64) / r)
+            inv_freq = exact.to(torch.float32)
+            self.inv_freq_lo = (exact - inv_freq.to(torch.float64)).to(torch.float32).to(rt.device)
         else:
             inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
         self.inv_freq: Optional[torch.Tensor] = inv_freq.to(rt.device)
@@ -67,6 +69,7 @@ class NoPosition:
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = 0
         self.inv_freq = None
+        self.inv_freq_lo = None
         self.interleaved = False
 
     def table(self, ctx: StepContext) -> None:

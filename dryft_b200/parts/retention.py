@@ -74,5 +74,6 @@ class Retention:
         proj = linear(h, self.w_in, self.rt)
         o = torch.empty((h.shape[0], self.n_heads * self.v_dim), dtype=h.dtype, device=h.device)
         K.retention_scan(proj, self.offsets, ctx.cu_q, ctx.seq_slot, ctx.tok_pos, self.position.inv_freq, self.position.rotary_dim,
-                         self.decay, state, o, ctx.n_seqs, self.n_heads, self.qk_dim, self.v_dim, self.k_scale, self.eps)
+                         self.decay, state, o, ctx.n_seqs, self.n_heads, self.qk_dim, self.v_dim, self.k_scale, self.eps,
+                         inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
         return linear(o, self.w_o, self.rt)

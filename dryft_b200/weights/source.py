@@ -100,6 +100,8 @@ def random_tensor(name: str, info: TensorInfo, seed: int, std: float, device: to
     mean = info.mean if info.mean is not None else (1.0 if info.kind == "vector" else 0.0)
     if mean:
         t += mean
+    if info.eye and len(info.shape) == 2 and info.shape[0] == info.shape[1]:
+        t += info.eye * torch.eye(info.shape[0], dtype=torch.float32, device=device)
     return t
 
 

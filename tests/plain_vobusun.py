@@ -113,9 +113,10 @@ def latent_attention(m: Mapping, p: str, tensors, h: torch.Tensor, eps: float) -
     dkv = h @ _t(tensors, p + "dkv").T
     c = rms_norm(dkv[:, :r], _t(tensors, p + "dkv.norm"), eps)
     k_rot = dkv[:, r:]
-    rot = m["rot"]
-    q_rot = rotate(q_rot, pos, rot["dims"], rot["base"], interleaved=True)
-    k_rot = rotate(k_rot, pos, rot["dims"], rot["base"], interleaved=True)
+    rot = m.get("rot")
+    if rot and dr:
+        q_rot = rotate(q_rot, pos, rot["dims"], rot["base"], interleaved=True)
+        k_rot = rotate(k_rot, pos, rot["dims"], rot["base"], interleaved=True)
     k_plain = (c @ _t(tensors, p + "uk").T).reshape(T, H, d)
     v = (c @ _t(tensors, p + "uv").T).reshape(T, H, dv)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
