@@ -46,8 +46,8 @@ template <typename T>
 __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
     const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int g_off, const int* __restrict__ cu_q,
     const int* __restrict__ seq_slot, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
-    const float* __restrict__ inv_freq_lo, int rot, const float* __restrict__ decay, float* __restrict__ state, T* __restrict__ out, int H, int dim, int vdim,
-    float k_scale, float eps) {
+    const float* __restrict__ inv_freq_lo, int rot, const double* __restrict__ decay, float* __restrict__ state,
+    T* __restrict__ out, int H, int dim, int vdim, float k_scale, float eps) {
   extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.x, hd = blockIdx.y;
   const int slot = seq_slot[b];
@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
   const int tid = threadIdx.x;
   float* Sg = state + ((size_t)slot * H + hd) * dim * vdim;
   for (int i = tid; i < dim * vdim; i += RT_THREADS) S[i] = Sg[i];
-  const float dec = decay[hd];
+  // the decay as a 32-bit value and what that drops: compounded over hundreds of tokens, one part in 2^24 of it shows
+  const float dec = (float)decay[hd], dec_lo = (float)(decay[hd] - (double)dec);
   const int half = rot >> 1;
   const int cv = tid % cols, rg = tid / cols;
   const bool active = rg < groups;
@@ -93,7 +94,8 @@ __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
         const float vv = vs[v];
         float acc = 0.f;
         for (int d = rg; d < dim; d += groups) {
-          const float s = fmaf(dec, S[d * vdim + v], ks[d] * vv);
+          const float old = S[d * vdim + v];
+          const float s = fmaf(dec, old, fmaf(dec_lo, old, ks[d] * vv));
           S[d * vdim + v] = s;
           acc = fmaf(s, qs[d], acc);
         }
@@ -117,6 +119,261 @@ __global__ void __launch_bounds__(RT_THREADS) retention_scan_kernel(
   }
   __syncthreads();
   for (int i = tid; i < dim * vdim; i += RT_THREADS) Sg[i] = S[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same retention for steps of many tokens, in chunks of CH tokens so that the work is matrix-shaped and spread over
+// (chunk, head) blocks instead of walked token by token.  For chunk g of a sequence, L tokens long, with S_in the state
+// before it (w = decay):
+//     D_g   = sum_j w^(L-1-j) k_j v_j^T                                   retention_chunk_state   (every chunk at once)
+//     S_in  of every chunk, by S <- w^L S + D_g in order                   retention_chunk_prefix  (elementwise; the
+//                                                                          sequence's stored state is read and updated)
+//     o_i   = w^(i+1) S_in^T q_i + sum_(j<=i) w^(i-j) (q_i . k_j) v_j       retention_chunk_out     (every chunk at once),
+// then the same norm and gate as above.  Powers of the decay come from a table made in 64-bit.  Chunk g of the step is
+// found from cu_q: sequence b has ceil(len_b / CH) chunks, numbered in sequence order after those of the sequences before.
+constexpr int CH = 64;
+constexpr int CK_THREADS = 256;
+
+__device__ __forceinline__ bool locate_chunk(const int* __restrict__ cu_q, int n_seqs, int g, int* b_out, int* k_out) {
+  int base = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    const int nc = (cu_q[b + 1] - cu_q[b] + CH - 1) / CH;
+    if (g < base + nc) { *b_out = b; *k_out = g - base; return true; }
+    base += nc;
+  }
+  return false;
+}
+
+// rows [L][ld] of shared memory <- the rotated (and scaled) head vectors of L tokens; columns dim..ld-1 are zeroed
+template <typename T>
+__device__ __forceinline__ void load_rotated(float* dst, int ld, const T* __restrict__ proj, int ldp, int col0, int n_first, int L,
+                                             int dim, int rot, const float* __restrict__ inv_freq,
+                                             const float* __restrict__ inv_freq_lo, const int* __restrict__ tok_pos, float scale) {
+  const int half = rot >> 1;
+  for (int idx = threadIdx.x; idx < L * ld; idx += CK_THREADS) {
+    const int t = idx / ld, d = idx % ld;
+    float val = 0.f;
+    if (d < dim) {
+      const T* src = proj + (size_t)(n_first + t) * ldp + col0;
+      val = to_f32<T>(src[d]);
+      if (d < rot) {
+        const int j = d < half ? d : d - half;
+        const float other = to_f32<T>(src[d < half ? d + half : d - half]);
+        float sn, cs;
+        sincos_split((float)tok_pos[n_first + t], inv_freq[j], inv_freq_lo ? inv_freq_lo[j] : 0.f, &sn, &cs);
+        val = d < half ? val * cs - other * sn : val * cs + other * sn;
+      }
+      val *= scale;
+    }
+    dst[t * ld + d] = val;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CK_THREADS) retention_chunk_state_kernel(
+    const T* __restrict__ proj, int ld, int k_off, int v_off, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+    int n_seqs, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
+    int rot, const double* __restrict__ decay, float* __restrict__ sbuf, int H, int dim, int vdim, float k_scale) {
+  extern __shared__ __align__(16) float smem[];
+  __shared__ int loc[3];
+  const int g = blockIdx.x, hd = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int b = 0, k = 0;
+    loc[2] = locate_chunk(cu_q, n_seqs, g, &b, &k) && seq_slot[b] >= 0;
+    loc[0] = b; loc[1] = k;
+  }
+  __syncthreads();
+  if (!loc[2]) return;
+  const int b = loc[0], n_first = cu_q[b] + loc[1] * CH, L = min(CH, cu_q[b + 1] - n_first);
+  const int dP = (dim + 7) & ~7, vP = (vdim + 7) & ~7;
+  float* ks = smem;                 // [CH][dP]
+  float* vs = ks + CH * dP;         // [CH][vP]
+  float* pw = vs + CH * vP;         // [CH + 1]
+  for (int i = threadIdx.x; i <= CH; i += CK_THREADS) pw[i] = (float)pow(decay[hd], (double)i);
+  load_rotated<T>(ks, dP, proj, ld, k_off + hd * dim, n_first, L, dim, rot, inv_freq, inv_freq_lo, tok_pos, k_scale);
+  for (int idx = threadIdx.x; idx < L * vP; idx += CK_THREADS) {
+    const int t = idx / vP, v = idx % vP;
+    vs[idx] = v < vdim ? to_f32<T>(proj[(size_t)(n_first + t) * ld + v_off + hd * vdim + v]) : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < L * dP; idx += CK_THREADS) ks[idx] *= pw[L - 1 - idx / dP];
+  __syncthreads();
+  float* dst = sbuf + ((size_t)g * H + hd) * dim * vdim;
+  const int tv = vP / 8, n_tiles = (dP / 8) * tv;
+  for (int tile = threadIdx.x; tile < n_tiles; tile += CK_THREADS) {
+    const int d0 = (tile / tv) * 8, v0 = (tile % tv) * 8;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
+    for (int j = 0; j < L; ++j) {
+      float kv[8], vv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { kv[i] = ks[j * dP + d0 + i]; vv[i] = vs[j * vP + v0 + i]; }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[i][c] = fmaf(kv[i], vv[c], acc[i][c]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (d0 + i < dim && v0 + c < vdim) dst[(size_t)(d0 + i) * vdim + v0 + c] = acc[i][c];
+  }
+}
+
+__global__ void retention_chunk_prefix_kernel(const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+                                              const double* __restrict__ decay, float* __restrict__ sbuf,
+                                              float* __restrict__ state, int H, int per_head) {
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  const int slot = seq_slot[b];
+  if (slot < 0 || e >= per_head) return;
+  int base = 0;
+  for (int bb = 0; bb < b; ++bb) base += (cu_q[bb + 1] - cu_q[bb] + CH - 1) / CH;
+  const int q = cu_q[b + 1] - cu_q[b];
+  float* sp = state + ((size_t)slot * H + hd) * per_head + e;
+  float S = *sp;
+  const double w = decay[hd];
+  const float w_full = (float)pow(w, (double)CH);
+  for (int k = 0; k * CH < q; ++k) {
+    float* cell = sbuf + ((size_t)(base + k) * H + hd) * per_head + e;
+    const float delta = *cell;
+    *cell = S;   // the state the chunk starts from
+    const int L = min(CH, q - k * CH);
+    S = fmaf(L == CH ? w_full : (float)pow(w, (double)L), S, delta);
+  }
+  *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CK_THREADS) retention_chunk_out_kernel(
+    const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int g_off, const int* __restrict__ cu_q,
+    const int* __restrict__ seq_slot, int n_seqs, const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
+    const float* __restrict__ inv_freq_lo, int rot, const double* __restrict__ decay, const float* __restrict__ sbuf,
+    T* __restrict__ out, int H, int dim, int vdim, float k_scale, float eps) {
+  extern __shared__ __align__(16) float smem[];
+  __shared__ int loc[3];
+  const int g = blockIdx.x, hd = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int b = 0, k = 0;
+    loc[2] = locate_chunk(cu_q, n_seqs, g, &b, &k) && seq_slot[b] >= 0;
+    loc[0] = b; loc[1] = k;
+  }
+  __syncthreads();
+  if (!loc[2]) return;
+  const int b = loc[0], n_first = cu_q[b] + loc[1] * CH, L = min(CH, cu_q[b + 1] - n_first);
+  const int dQ = ((dim + 3) & ~3) + 1;           // odd row length: rows of q and k fall on different banks
+  const int vP = (vdim + 3) & ~3;
+  const int stage = max(CH * dQ, CH * vP);       // the q rows' place also holds the outputs before the norm
+  float* qs = smem;                  // [CH][dQ], later o [CH][vP]
+  float* ks = qs + stage;            // [CH][dQ]
+  float* vs = ks + CH * dQ;          // [CH][vP]
+  float* A = vs + CH * vP;           // [CH][CH + 1]
+  float* pw = A + CH * (CH + 1);     // [CH + 1]
+  for (int i = threadIdx.x; i <= CH; i += CK_THREADS) pw[i] = (float)pow(decay[hd], (double)i);
+  load_rotated<T>(qs, dQ, proj, ld, q_off + hd * dim, n_first, L, dim, rot, inv_freq, inv_freq_lo, tok_pos, 1.f);
+  load_rotated<T>(ks, dQ, proj, ld, k_off + hd * dim, n_first, L, dim, rot, inv_freq, inv_freq_lo, tok_pos, k_scale);
+  for (int idx = threadIdx.x; idx < CH * vP; idx += CK_THREADS) {
+    const int t = idx / vP, v = idx % vP;
+    vs[idx] = (t < L && v < vdim) ? to_f32<T>(proj[(size_t)(n_first + t) * ld + v_off + hd * vdim + v]) : 0.f;
+  }
+  for (int idx = threadIdx.x + L * dQ; idx < CH * dQ; idx += CK_THREADS) { qs[idx] = 0.f; ks[idx] = 0.f; }   // rows behind the chunk
+  __syncthreads();
+  // A[i][j] = w^(i-j) q_i . k_j  for j <= i, else 0: 4 x 4 outputs a thread
+  for (int tile = threadIdx.x; tile < (CH / 4) * (CH / 4); tile += CK_THREADS) {
+    const int i0 = (tile / (CH / 4)) * 4, j0 = (tile % (CH / 4)) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+    if (j0 <= i0 + 3 && i0 < L) {
+      for (int d = 0; d < dim; ++d) {
+        float qv[4], kv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) { qv[r] = qs[(i0 + r) * dQ + d]; kv[r] = ks[(j0 + r) * dQ + d]; }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(qv[r], kv[c], acc[r][c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = i0 + r, j = j0 + c;
+        A[i * (CH + 1) + j] = j <= i ? acc[r][c] * pw[i - j] : 0.f;
+      }
+  }
+  __syncthreads();
+  // o = w^(i+1) (q S_in) + A v : 8 rows x 4 columns a thread, kept in registers until every thread has read q
+  const float* S_in = sbuf + ((size_t)g * H + hd) * dim * vdim;
+  const int tv = vP / 4, n_tiles = (CH / 8) * tv;
+  constexpr int MAX_TILES = 4;       // tiles a thread may hold (value sizes up to 512)
+  float acc[MAX_TILES][8][4];
+  int n_mine = 0;
+  for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
+    const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
+    float (*a)[4] = acc[n_mine];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[r][c] = 0.f;
+    if (i0 >= L) continue;
+    for (int d = 0; d < dim; ++d) {
+      float sv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sv[c] = v0 + c < vdim ? __ldg(S_in + (size_t)d * vdim + v0 + c) : 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float qv = qs[(i0 + r) * dQ + d];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) a[r][c] = fmaf(qv, sv[c], a[r][c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[r][c] *= pw[i0 + r + 1];
+    const int j_end = min(L, i0 + 8);
+    for (int j = 0; j < j_end; ++j) {
+      float vv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) vv[c] = vs[j * vP + v0 + c];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float av = A[(i0 + r) * (CH + 1) + j];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) a[r][c] = fmaf(av, vv[c], a[r][c]);
+      }
+    }
+  }
+  __syncthreads();   // q is read by all: its place takes the outputs
+  n_mine = 0;
+  for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
+    const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) qs[(i0 + r) * vP + v0 + c] = acc[n_mine][r][c];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = warp; i < L; i += CK_THREADS / 32) {
+    float ss = 0.f;
+    for (int v = lane; v < vdim; v += 32) { const float o = qs[i * vP + v]; ss = fmaf(o, o, ss); }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)vdim + eps);
+    const size_t n = (size_t)(n_first + i);
+    for (int v = lane; v < vdim; v += 32) {
+      const float gv = to_f32<T>(proj[n * ld + g_off + hd * vdim + v]);
+      out[n * H * vdim + hd * vdim + v] = from_f32<T>(qs[i * vP + v] * inv * (gv / (1.f + expf(-gv))));
+    }
+  }
 }
 
 constexpr int GT = 8;          // tokens per block of rglru_gates
@@ -226,7 +483,7 @@ template <typename K> int opt_in_smem(K kernel, size_t bytes) {
 
 DRYFT_API int dryft_retention_scan(int is_bf16, const void* proj, int ld, int q_off, int k_off, int v_off, int g_off,
                                    const int* cu_q, const int* seq_slot, const int* tok_pos, const float* inv_freq,
-                                   const float* inv_freq_lo, int rot, const float* decay, float* state, void* out, int n_seqs, int H, int dim, int vdim,
+                                   const float* inv_freq_lo, int rot, const double* decay, float* state, void* out, int n_seqs, int H, int dim, int vdim,
                                    float k_scale, float eps, cudaStream_t st) {
   if (n_seqs <= 0) return 0;
   if (H <= 0 || dim <= 0 || vdim <= 0 || rot < 0 || rot > dim || (rot & 1) || H > 65535) return DRYFT_ERR_UNSUPPORTED;
@@ -245,6 +502,54 @@ DRYFT_API int dryft_retention_scan(int is_bf16, const void* proj, int ld, int q_
                                                                  k_scale, eps);
   return launch_status();
 }
+
+// The chunked form: `sbuf` holds (n_tokens / CH + n_seqs) * H * dim * vdim floats.  Three launches.
+DRYFT_API int dryft_retention_chunked(int is_bf16, const void* proj, int ld, int q_off, int k_off, int v_off, int g_off,
+                                      const int* cu_q, const int* seq_slot, const int* tok_pos, const float* inv_freq,
+                                      const float* inv_freq_lo, int rot, const double* decay, float* state, float* sbuf,
+                                      void* out, int n_tokens, int n_seqs, int H, int dim, int vdim, float k_scale, float eps,
+                                      cudaStream_t st) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (H <= 0 || dim <= 0 || vdim <= 0 || vdim > 512 || rot < 0 || rot > dim || (rot & 1) || H > 65535 || n_seqs > 65535)
+    return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int n_chunks = n_tokens / CH + n_seqs;       // an upper bound; blocks behind the last chunk leave at once
+  const int dP = (dim + 7) & ~7, vP8 = (vdim + 7) & ~7;
+  const size_t smem_a = sizeof(float) * ((size_t)CH * dP + (size_t)CH * vP8 + CH + 1);
+  const int dQ = ((dim + 3) & ~3) + 1, vP = (vdim + 3) & ~3;
+  const size_t stage = (size_t)CH * (dQ > vP ? dQ : vP);
+  const size_t smem_c = sizeof(float) * (stage + (size_t)CH * dQ + (size_t)CH * vP + (size_t)CH * (CH + 1) + CH + 1);
+  int rc = is_bf16 ? opt_in_smem(retention_chunk_state_kernel<bf>, smem_a) : opt_in_smem(retention_chunk_state_kernel<float>, smem_a);
+  if (rc) return rc;
+  rc = is_bf16 ? opt_in_smem(retention_chunk_out_kernel<bf>, smem_c) : opt_in_smem(retention_chunk_out_kernel<float>, smem_c);
+  if (rc) return rc;
+  dim3 grid(n_chunks, H);
+  if (is_bf16)
+    retention_chunk_state_kernel<bf><<<grid, CK_THREADS, smem_a, st>>>((const bf*)proj, ld, k_off, v_off, cu_q, seq_slot, n_seqs, tok_pos,
+                                                                       inv_freq, inv_freq_lo, rot, decay, sbuf, H, dim, vdim, k_scale);
+  else
+    retention_chunk_state_kernel<float><<<grid, CK_THREADS, smem_a, st>>>((const float*)proj, ld, k_off, v_off, cu_q, seq_slot, n_seqs,
+                                                                          tok_pos, inv_freq, inv_freq_lo, rot, decay, sbuf, H, dim, vdim,
+                                                                          k_scale);
+  int e = launch_status();
+  if (e) return e;
+  const int per_head = dim * vdim;
+  dim3 grid_b(n_seqs, H, (per_head + 255) / 256);
+  retention_chunk_prefix_kernel<<<grid_b, 256, 0, st>>>(cu_q, seq_slot, decay, sbuf, state, H, per_head);
+  e = launch_status();
+  if (e) return e;
+  if (is_bf16)
+    retention_chunk_out_kernel<bf><<<grid, CK_THREADS, smem_c, st>>>((const bf*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot, n_seqs,
+                                                                     tok_pos, inv_freq, inv_freq_lo, rot, decay, sbuf, (bf*)out, H, dim,
+                                                                     vdim, k_scale, eps);
+  else
+    retention_chunk_out_kernel<float><<<grid, CK_THREADS, smem_c, st>>>((const float*)proj, ld, q_off, k_off, v_off, g_off, cu_q, seq_slot,
+                                                                        n_seqs, tok_pos, inv_freq, inv_freq_lo, rot, decay, sbuf,
+                                                                        (float*)out, H, dim, vdim, k_scale, eps);
+  return launch_status();
+}
+
+DRYFT_API int dryft_retention_chunk_tokens() { return CH; }
 
 DRYFT_API int dryft_rglru_gates(int is_bf16, const void* proj, int ld, int x_off, const float* x_bias, const int* tok_slot,
                                 const float* conv_w, const float* conv_b, int taps, const float* tail, const float* w_gates,

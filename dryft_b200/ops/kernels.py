@@ -1218,6 +1218,8 @@ def stream_hc_lib() -> ctypes.CDLL:
 def recurrent_lib() -> ctypes.CDLL:
     """Mixers with a fixed-size 32-bit state per sequence: retention, gated linear recurrence."""
     return _single_lib("recurrent", {
+        "dryft_retention_chunked": [_i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
+        "dryft_retention_chunk_tokens": [],
         "dryft_retention_scan": [_i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p],
         "dryft_rglru_gates": [_i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _f, _p, _p, _i, _i, _i, _p],
         "dryft_rglru_scan": [_i, _p, _i, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p],
@@ -1337,13 +1339,17 @@ def _freq_lo(inv_freq_lo, rot: int):
     return None
 
 
+RETENTION_CHUNKED_MAX_VDIM = 512   # value sizes the chunked form holds in a thread's registers
+
+
 def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, decay, state, out, n_seqs: int, heads: int,
-                   dim: int, vdim: int, k_scale: float, eps: float, inv_freq_lo=None) -> None:
+                   dim: int, vdim: int, k_scale: float, eps: float, inv_freq_lo=None, chunked: bool = False) -> None:
     """``inv_freq_lo`` (optional, here and in the latent attention wrappers): the part of each frequency that its 32-bit
     value drops; with it the angles are as exact as the pair.
 
     Retention over the step's tokens from and to ``state [slots, heads, dim, vdim]`` (float32).  ``proj [n, ld]`` holds
-    q | k | v | g at the column ``offsets`` (4 ints); ``out [n, heads * vdim]``."""
+    q | k | v | g at the column ``offsets`` (4 ints); ``out [n, heads * vdim]``; ``decay [heads]`` float64.  ``chunked``:
+    the form for steps of many tokens (the same result up to rounding; token by token otherwise)."""
     n, ld = proj.shape
     _need(proj, "proj")
     q_off, k_off, v_off, g_off = (int(o) for o in offsets)
@@ -1353,9 +1359,19 @@ def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, d
         _need(t, nm, torch.int32)
     if rot:
         _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
-    _need(decay, "decay", torch.float32, (heads,))
+    _need(decay, "decay", torch.float64, (heads,))
     _need(state, "state", torch.float32, (None, heads, dim, vdim))
     _need(out, "out", proj.dtype, (n, heads * vdim))
+    if chunked and vdim <= RETENTION_CHUNKED_MAX_VDIM:
+        # steps of many tokens: chunk states, their prefix, chunk outputs (three launches, the work spread over chunks)
+        lib = recurrent_lib()
+        ch = int(lib.dryft_retention_chunk_tokens())
+        sbuf = torch.empty((n // ch + n_seqs) * heads * dim * vdim, dtype=torch.float32, device=proj.device)
+        _ok(lib.dryft_retention_chunked(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
+                                        _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state),
+                                        _ptr(sbuf), _ptr(out), n, n_seqs, heads, dim, vdim, float(k_scale), float(eps), _stream()),
+            f"retention_chunked ({heads} heads of {dim} x {vdim})", n_kernels=3)
+        return
     _ok(recurrent_lib().dryft_retention_scan(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
                                              _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state), _ptr(out), n_seqs,
                                              heads, dim, vdim, float(k_scale), float(eps), _stream()),

@@ -52,7 +52,7 @@ class Retention:
         decay = [float(d) for d in params["decay"]]
         if len(decay) != self.n_heads:
             raise ValueError(f"retention: {len(decay)} decays for {self.n_heads} heads")
-        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(rt.device)
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(rt.device)   # 64-bit: the kernels split it into a pair
         pos: PartSpec = params.get("position") or PartSpec("none")
         self.position = POSITIONS.get(pos.kind)(pos.params, self.qk_dim, rt)
         if getattr(self.position, "interleaved", False):
@@ -75,5 +75,5 @@ class Retention:
         o = torch.empty((h.shape[0], self.n_heads * self.v_dim), dtype=h.dtype, device=h.device)
         K.retention_scan(proj, self.offsets, ctx.cu_q, ctx.seq_slot, ctx.tok_pos, self.position.inv_freq, self.position.rotary_dim,
                          self.decay, state, o, ctx.n_seqs, self.n_heads, self.qk_dim, self.v_dim, self.k_scale, self.eps,
-                         inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
+                         inv_freq_lo=getattr(self.position, "inv_freq_lo", None), chunked=not ctx.decode)
         return linear(o, self.w_o, self.rt)

@@ -129,8 +129,9 @@ def test_retention_keeps_one_far_key_among_hundreds_and_splits_anywhere(H, d, dv
         exact = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64)
         inv = exact.float().to(DEV)
         inv_lo = (exact - exact.float().double()).float().to(DEV)
-    dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
-    for cuts in ([T], [1, 2, 64, 65, 300, T]):             # whole, and in pieces (one token, two, across any edge)
+    dec = torch.tensor(decay, dtype=torch.float64, device=DEV)
+    # whole, and in pieces (one token, two, across any edge); token by token and in the chunked form
+    for cuts, chunked in (([T], False), ([T], True), ([1, 2, 64, 65, 300, T], False), ([1, 3, 64, 129, 131, 300, T], True)):
         state = torch.full((3, H, d, dv), float("nan"), device=DEV)
         state[1] = 0.0                                     # the sequence's slot starts at zero; the others hold rubbish
         out = torch.empty(T, H * dv, device=DEV)
@@ -139,11 +140,11 @@ def test_retention_keeps_one_far_key_among_hundreds_and_splits_anywhere(H, d, dv
             pos = torch.arange(lo, hi, dtype=torch.int32, device=DEV)
             piece = torch.empty(hi - lo, H * dv, device=DEV)
             K.retention_scan(proj[lo:hi].contiguous(), offs, i32([0, hi - lo]), i32([1]), pos, inv, rot, dec, state, piece, 1, H, d, dv,
-                             d ** -0.5, eps, inv_freq_lo=inv_lo)
+                             d ** -0.5, eps, inv_freq_lo=inv_lo, chunked=chunked)
             out[lo:hi] = piece
             lo = hi
         err = (out.double().cpu() - want).abs().max() / want.abs().max()
-        assert float(err) < 2e-5, (cuts, float(err))
+        assert float(err) < 2e-5, (cuts, chunked, float(err))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -238,3 +239,30 @@ def test_gated_recurrence_tail_across_cuts_shorter_than_the_taps():
     for b in range(2):
         err = (got[b].double().cpu() - want[b]).abs().max() / want[b].abs().max()
         assert float(err) < 1e-5, (b, float(err))
+
+
+def test_retention_chunked_with_several_sequences_of_unequal_lengths():
+    """Three sequences in one step (one of a single token, one that ends on a chunk's edge) from states of their own."""
+    H, d, dv, rot, eps = 2, 24, 40, 12, 1e-6
+    decay = [0.97, 0.9995]
+    lens, starts = [1, 128, 77], [5, 0, 300]
+    inv = torch.tensor([100.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64)
+    rows, pos, cu = [], [], [0]
+    for n, s0 in zip(lens, starts):
+        rows.append(torch.randn(n, 2 * H * d + 2 * H * dv, dtype=torch.float64) * 0.5)
+        pos += list(range(s0, s0 + n))
+        cu.append(cu[-1] + n)
+    proj = torch.cat(rows).float().to(DEV).contiguous()
+    state0 = torch.randn(4, H, d, dv, device=DEV)
+    args = dict(inv_freq_lo=(inv - inv.float().double()).float().to(DEV))
+    offs = (0, H * d, 2 * H * d, 2 * H * d + H * dv)
+    outs = []
+    for chunked in (False, True):
+        state = state0.clone()
+        out = torch.empty(proj.shape[0], H * dv, device=DEV)
+        K.retention_scan(proj, offs, i32(cu), i32([2, 0, 3]), i32(pos), inv.float().to(DEV), rot, torch.tensor(decay, dtype=torch.float64, device=DEV),
+                         state, out, 3, H, d, dv, d ** -0.5, eps, chunked=chunked, **args)
+        outs.append((out, state))
+    assert torch.equal(outs[0][1][1], state0[1])                       # a slot no sequence of the step holds
+    assert torch.allclose(outs[0][0], outs[1][0], atol=2e-5, rtol=2e-5)
+    assert torch.allclose(outs[0][1], outs[1][1], atol=2e-5, rtol=2e-5)
