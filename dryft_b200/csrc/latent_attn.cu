@@ -8,10 +8,11 @@
 //                      cq = T( rmsnorm(dq) * w_q )                        -> the query up-projection's input
 //                      c  = rmsnorm(dkv[:kv_rank]) * w_kv ; k_rot = rotate(dkv[kv_rank:]) at the token's position
 //                      cache row (slot, position) <- T([c | k_rot])
-// latent_attn_rows   one block per (query token, group of heads), a warp per head.  Keys position-window+1 .. position
-//                    (all keys from 0 if window is 0) are staged 32 at a time in shared memory as floats; a lane takes a
-//                    key for the scores (softmax running maximum and sum in 32-bit) and a slice of the latent for the
-//                    weighted sum.  The query's rotated part is rotated here.  Heads-major input and output:
+// latent_attn_rows   one block per (query token, group of heads, split of the keys), a warp per head.  Keys
+//                    position-window+1 .. position (all keys from 0 if window is 0) are staged 32 at a time in shared memory
+//                    as floats (16-byte loads, several in flight per thread); a lane takes a key for the scores (softmax
+//                    running maximum and sum in 32-bit) and a slice of the latent for the weighted sum.  A step of few
+//                    tokens splits each token's keys over several blocks, joined by latent_combine.  The query's rotated part is rotated here.  Heads-major input and output:
 //                    q_lat [H, N, kv_rank] (32-bit), q [N, H, q_stride] with the rotated part at q_rot_off,
 //                    o_lat [H, N, kv_rank].
 // head_gate          out[n, h, :] = T( o[h, n, :] * sigmoid(gate_logit[n, h]) )
@@ -24,7 +25,7 @@
 
 namespace {
 constexpr int PREP_THREADS = 256;
-constexpr int HPB = 4;         // heads (warps) per block of latent_attn_rows
+constexpr int HPB = 8;         // heads (warps) per block of latent_attn_rows
 constexpr int KT = 32;         // keys per staged tile
 
 // sin and cos of  pos * (f_hi + f_lo)  for a rotary position: the product is formed in 32-bit, and what its rounding
@@ -87,24 +88,49 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
     dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
 }
 
+// 16 bytes of a cached row as floats (8 bfloat16 or 4 float)
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& raw, float* out) {
+    out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y); out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& raw, float* out) {
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { out[2 * i] = __uint_as_float(w[i] << 16); out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+
+// One block per (query token, group of HPB heads, split of the visible keys).  With one split the result goes to o_lat;
+// with several, each block leaves (max, sum, unnormalised weighted sum) in `part` and latent_combine joins them.
 template <typename T, int NR>
 __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
     const float* __restrict__ q_lat, const T* __restrict__ q, int q_stride, int q_rot_off, const T* __restrict__ k_pages,
     const int* __restrict__ page_table, int max_pages, int page_size, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
-    int interleaved, T* __restrict__ o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window) {
+    int interleaved, T* __restrict__ o_lat, float* __restrict__ part, int n_splits, int n_tokens, int H, int kv_rank, int rot,
+    float scale, int window) {
   extern __shared__ __align__(16) float sm[];
   const int Dk = kv_rank + rot, Dp = Dk + 1;
   float* tile = sm;                                  // [KT][Dp]
   float* qs_all = tile + (size_t)KT * Dp;            // [HPB][Dk]
   float* raw = qs_all + (size_t)HPB * Dk;            // [HPB][rot]
-  const int n = blockIdx.x;
+  const int n = blockIdx.x, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hd = blockIdx.y * HPB + warp;
   const int slot = tok_slot[n];
   if (slot < 0) return;
   const int pos = tok_pos[n];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo_all = window > 0 ? max(0, pos - window + 1) : 0;
+  // this split's share of the key tiles (whole tiles, in order)
+  const int tiles_all = (pos - lo_all) / KT + 1;
+  const int per_split = (tiles_all + n_splits - 1) / n_splits;
+  const int lo = lo_all + split * per_split * KT;
+  const int hi = min(pos, lo + per_split * KT - 1);   // last key of this split
   const bool live = hd < H;
   float* qs = qs_all + (size_t)warp * Dk;
   if (live) {
@@ -121,22 +147,59 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
 #pragma unroll
   for (int r = 0; r < NR; ++r) acc[r] = 0.f;
   const int* pt = page_table + (size_t)slot * max_pages;
-  for (int j0 = lo; j0 <= pos; j0 += KT) {
-    const int cnt = min(KT, pos - j0 + 1);
+  constexpr int VN = Vec16<T>::N;
+  const bool vec_ok = (Dk % VN) == 0;     // rows start on 16-byte boundaries
+  const int vpr = Dk / VN;
+  for (int j0 = lo; j0 <= hi; j0 += KT) {
+    const int cnt = min(KT, hi - j0 + 1);
     __syncthreads();   // the tile before is used up (and, the first time, qs is written)
-    for (int kk = warp; kk < cnt; kk += HPB) {
-      const int j = j0 + kk;
-      const T* src = k_pages + ((size_t)pt[j / page_size] * page_size + j % page_size) * Dk;
-      for (int d = lane; d < Dk; d += 32) tile[kk * Dp + d] = to_f32<T>(src[d]);
+    if (vec_ok) {
+      // every thread asks for four 16-byte pieces before it unpacks the first: the loads' round trips overlap
+      const int total = cnt * vpr;
+      for (int base = threadIdx.x; base < total; base += 4 * HPB * 32) {
+        uint4 v[4];
+        int at[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * HPB * 32;
+          at[u] = -1;
+          if (idx < total) {
+            const int kk = idx / vpr, c = idx - kk * vpr, j = j0 + kk;
+            const T* src = k_pages + ((size_t)pt[j / page_size] * page_size + j % page_size) * Dk;
+            v[u] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+            at[u] = kk * Dp + c * VN;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (at[u] >= 0) {
+            float f[VN];
+            Vec16<T>::unpack(v[u], f);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) tile[at[u] + e] = f[e];
+          }
+        }
+      }
+    } else {
+      for (int kk = warp; kk < cnt; kk += HPB) {
+        const int j = j0 + kk;
+        const T* src = k_pages + ((size_t)pt[j / page_size] * page_size + j % page_size) * Dk;
+        for (int d = lane; d < Dk; d += 32) tile[kk * Dp + d] = to_f32<T>(src[d]);
+      }
     }
     __syncthreads();
     if (!live) continue;
     float s = -INFINITY;
     if (lane < cnt) {
       const float* kr = tile + lane * Dp;
-      float a = 0.f;
-      for (int d = 0; d < Dk; ++d) a = fmaf(qs[d], kr[d], a);
-      s = a;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;   // four chains instead of one
+      int d = 0;
+      for (; d + 3 < Dk; d += 4) {
+        a0 = fmaf(qs[d], kr[d], a0); a1 = fmaf(qs[d + 1], kr[d + 1], a1);
+        a2 = fmaf(qs[d + 2], kr[d + 2], a2); a3 = fmaf(qs[d + 3], kr[d + 3], a3);
+      }
+      for (; d < Dk; ++d) a0 = fmaf(qs[d], kr[d], a0);
+      s = (a0 + a1) + (a2 + a3);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = lane < cnt ? expf(s - m_new) : 0.f;
@@ -156,12 +219,47 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
     m = m_new;
   }
   if (!live) return;
+  if (n_splits > 1) {   // a split without keys leaves max = -inf, sum = 0
+    float* dst = part + (((size_t)n * H + hd) * n_splits + split) * (kv_rank + 2);
+    if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const int d = lane + 32 * r;
+      if (d < kv_rank) dst[2 + d] = acc[r];
+    }
+    return;
+  }
   T* dst = o_lat + ((size_t)hd * n_tokens + n) * kv_rank;
   const float inv = 1.f / l;
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
     const int d = lane + 32 * r;
     if (d < kv_rank) dst[d] = from_f32<T>(acc[r] * inv);
+  }
+}
+
+// o_lat[h, n, :] from the splits' (max, sum, weighted sum): one block per (token, head)
+template <typename T>
+__global__ void latent_combine_kernel(const float* __restrict__ part, const int* __restrict__ tok_slot, T* __restrict__ o_lat,
+                                      int n_splits, int n_tokens, int H, int kv_rank) {
+  const int n = blockIdx.x, hd = blockIdx.y;
+  if (tok_slot[n] < 0) return;
+  const float* src = part + ((size_t)n * H + hd) * n_splits * (kv_rank + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[(size_t)s * (kv_rank + 2)]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = src[(size_t)s * (kv_rank + 2)];
+    if (ms > -INFINITY) l += src[(size_t)s * (kv_rank + 2) + 1] * expf(ms - m);
+  }
+  const float inv = 1.f / l;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = src[(size_t)s * (kv_rank + 2)];
+      if (ms > -INFINITY) a = fmaf(src[(size_t)s * (kv_rank + 2) + 2 + d], expf(ms - m), a);
+    }
+    o_lat[((size_t)hd * n_tokens + n) * kv_rank + d] = from_f32<T>(a * inv);
   }
 }
 
@@ -193,15 +291,20 @@ template <typename K> int opt_in(K kernel, size_t bytes) {
 template <typename T, int NR>
 int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, const void* k_pages, const int* page_table,
                 int max_pages, int page_size, const int* tok_slot, const int* tok_pos, const float* inv_freq,
-                const float* inv_freq_lo, int interleaved, void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+                const float* inv_freq_lo, int interleaved, void* o_lat, float* part, int n_splits, int n_tokens, int H, int kv_rank,
+                int rot, float scale, int window, cudaStream_t st) {
   const int Dk = kv_rank + rot;
   const size_t smem = sizeof(float) * ((size_t)KT * (Dk + 1) + (size_t)HPB * Dk + (size_t)HPB * rot);
   int rc = opt_in(latent_attn_rows_kernel<T, NR>, smem);
   if (rc) return rc;
-  dim3 grid(n_tokens, (H + HPB - 1) / HPB);
+  dim3 grid(n_tokens, (H + HPB - 1) / HPB, n_splits);
   latent_attn_rows_kernel<T, NR><<<grid, HPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
                                                                max_pages, page_size, tok_slot, tok_pos, inv_freq, inv_freq_lo,
-                                                               interleaved, (T*)o_lat, n_tokens, H, kv_rank, rot, scale, window);
+                                                               interleaved, (T*)o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale,
+                                                               window);
+  int e = launch_status();
+  if (e || n_splits <= 1) return e;
+  latent_combine_kernel<T><<<dim3(n_tokens, H), 128, 0, st>>>(part, tok_slot, (T*)o_lat, n_splits, n_tokens, H, kv_rank);
   return launch_status();
 }
 }  // namespace
@@ -229,16 +332,19 @@ DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_of
 DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void* q, int q_stride, int q_rot_off,
                                      const void* k_pages, const int* page_table, int max_pages, int page_size,
                                      const int* tok_slot, const int* tok_pos, const float* inv_freq, const float* inv_freq_lo,
-                                     int interleaved, void* o_lat, int n_tokens, int H, int kv_rank, int rot, float scale, int window, cudaStream_t st) {
+                                     int interleaved, void* o_lat, float* part, int n_splits, int n_tokens, int H, int kv_rank,
+                                     int rot, float scale, int window, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (kv_rank <= 0 || kv_rank > 512 || rot < 0 || (rot & 1) || H <= 0 || (H + HPB - 1) / HPB > 65535) return DRYFT_ERR_UNSUPPORTED;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && !part)) return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
   const int nr = (kv_rank + 31) / 32;
 #define DRYFT_LATENT_ROWS(NR)                                                                                                      \
   return is_bf16 ? launch_rows<bf, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot, tok_pos,  \
-                                       inv_freq, inv_freq_lo, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)                \
+                                       inv_freq, inv_freq_lo, interleaved, o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale, window, st) \
                  : launch_rows<float, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot,      \
-                                          tok_pos, inv_freq, inv_freq_lo, interleaved, o_lat, n_tokens, H, kv_rank, rot, scale, window, st)
+                                          tok_pos, inv_freq, inv_freq_lo, interleaved, o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale, \
+                                          window, st)
   if (nr <= 1) { DRYFT_LATENT_ROWS(1); }
   if (nr <= 2) { DRYFT_LATENT_ROWS(2); }
   if (nr <= 4) { DRYFT_LATENT_ROWS(4); }

@@ -238,12 +238,20 @@ __global__ void retention_chunk_prefix_kernel(const int* __restrict__ cu_q, cons
   float S = *sp;
   const double w = decay[hd];
   const float w_full = (float)pow(w, (double)CH);
-  for (int k = 0; k * CH < q; ++k) {
-    float* cell = sbuf + ((size_t)(base + k) * H + hd) * per_head + e;
-    const float delta = *cell;
-    *cell = S;   // the state the chunk starts from
-    const int L = min(CH, q - k * CH);
-    S = fmaf(L == CH ? w_full : (float)pow(w, (double)L), S, delta);
+  const int n_chunks = (q + CH - 1) / CH;
+  for (int k0 = 0; k0 < n_chunks; k0 += 8) {   // eight chunk sums asked for at once, then folded in order
+    float delta[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (k0 + u < n_chunks) delta[u] = __ldcs(sbuf + ((size_t)(base + k0 + u) * H + hd) * per_head + e);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (k0 + u < n_chunks) {
+        sbuf[((size_t)(base + k0 + u) * H + hd) * per_head + e] = S;   // the state the chunk starts from
+        const int L = min(CH, q - (k0 + u) * CH);
+        S = fmaf(L == CH ? w_full : (float)pow(w, (double)L), S, delta[u]);
+      }
+    }
   }
   *sp = S;
 }
@@ -455,10 +463,23 @@ __global__ void rglru_scan_kernel(const T* __restrict__ proj, int ld, int y_off,
   const int n0 = cu_q[b], n1 = cu_q[b + 1];
   float S = state[(size_t)slot * C + c];
   const float yb = y_bias[c];
-  for (int n = n0; n < n1; ++n) {
-    S = fmaf(a_in[(size_t)n * C + c], S, b_in[(size_t)n * C + c]);
-    const float yv = gelu_tanh_f(to_f32<T>(proj[(size_t)n * ld + y_off + c]) + yb);
-    out[(size_t)n * C + c] = from_f32<T>(S * yv);
+  for (int nb = n0; nb < n1; nb += 8) {   // eight tokens' inputs asked for at once, then folded in order
+    float av[8], bv[8], yv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (nb + u < n1) {
+        av[u] = a_in[(size_t)(nb + u) * C + c];
+        bv[u] = b_in[(size_t)(nb + u) * C + c];
+        yv[u] = to_f32<T>(proj[(size_t)(nb + u) * ld + y_off + c]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (nb + u < n1) {
+        S = fmaf(av[u], S, bv[u]);
+        out[(size_t)(nb + u) * C + c] = from_f32<T>(S * gelu_tanh_f(yv[u] + yb));
+      }
+    }
   }
   state[(size_t)slot * C + c] = S;
   const int K1 = taps - 1, q = n1 - n0;

@@ -78,6 +78,24 @@ __global__ void seq_last_token_kernel(const int* __restrict__ tokens, const int*
   if (n + 1 == n_tokens || tok_slot[n + 1] != slot) prev_state[slot] = tokens[n];
 }
 
+// four consecutive elements at once (8 or 16 bytes)
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS) hc_step_kernel(
     const float* __restrict__ x_in, int s_in, float* __restrict__ x_out, int S, const T* __restrict__ y,
@@ -95,6 +113,60 @@ __global__ void __launch_bounds__(THREADS) hc_step_kernel(
   }
   __syncthreads();
   float ss = 0.f;
+  if ((width & 3) == 0) {
+    // four columns a thread, 16-byte accesses to the streams: the pass is bound by bytes in flight
+    for (int c = threadIdx.x * 4; c < width; c += THREADS * 4) {
+      float4 x[MAX_STREAMS];
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) x[s] = *reinterpret_cast<const float4*>(x_in + (src * s_in + (s_in == 1 ? 0 : s)) * width + c);
+      if (y) {
+        const float4 yv = load4<T>(y + src * width + c);
+        float4 xn[MAX_STREAMS];
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t) {
+          if (t < S) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+              if (s < S) {
+                const float m = c_mix[s * S + t];
+                acc.x = fmaf(m, x[s].x, acc.x); acc.y = fmaf(m, x[s].y, acc.y); acc.z = fmaf(m, x[s].z, acc.z); acc.w = fmaf(m, x[s].w, acc.w);
+              }
+            const float o = c_out[t];
+            xn[t] = make_float4(fmaf(o, yv.x, acc.x), fmaf(o, yv.y, acc.y), fmaf(o, yv.z, acc.z), fmaf(o, yv.w, acc.w));
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t)
+          if (t < S) x[t] = xn[t];
+      }
+      if (x_out) {
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t)
+          if (t < S) *reinterpret_cast<float4*>(x_out + (src * S + t) * width + c) = x[t];
+      }
+      if (inw) {
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t)
+          if (t < S) {
+            const float w = c_in[t];
+            u.x = fmaf(w, x[t].x, u.x); u.y = fmaf(w, x[t].y, u.y); u.z = fmaf(w, x[t].z, u.z); u.w = fmaf(w, x[t].w, u.w);
+          }
+        *reinterpret_cast<float4*>(row + c) = u;
+        ss = fmaf(u.x, u.x, fmaf(u.y, u.y, fmaf(u.z, u.z, fmaf(u.w, u.w, ss))));
+      }
+    }
+    if (!inw) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x * 4; c < width; c += THREADS * 4) {
+      const float4 u = *reinterpret_cast<const float4*>(row + c), w = *reinterpret_cast<const float4*>(norm_w + c);
+      store4<T>(h + (size_t)r * width + c, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < width; c += THREADS) {
     float x[MAX_STREAMS];
 #pragma unroll

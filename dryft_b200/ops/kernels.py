@@ -1230,7 +1230,7 @@ def latent_attn_lib() -> ctypes.CDLL:
     """Attention over cached low-rank latents."""
     return _single_lib("latent_attn", {
         "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p],
-        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p],
+        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
         "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
     })
 
@@ -1435,9 +1435,10 @@ def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int,
 
 
 def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, tok_pos, inv_freq, interleaved: bool, o_lat,
-                     kv_rank: int, rot: int, scale: float, window: Optional[int], inv_freq_lo=None) -> None:
+                     kv_rank: int, rot: int, scale: float, window: Optional[int], inv_freq_lo=None, n_splits: int = 1) -> None:
     """``o_lat [H, n, kv_rank]``: softmax attention of ``q_lat [H, n, kv_rank]`` (float32, the key matrices folded in) and the
-    rotated part of ``q [n, H, q_stride]`` (at ``q_rot_off``, rotated here) over the cached rows ``[c | k_rot]``."""
+    rotated part of ``q [n, H, q_stride]`` (at ``q_rot_off``, rotated here) over the cached rows ``[c | k_rot]``.
+    ``n_splits``: blocks that share each token's visible keys (whole tiles of 32 keys each)."""
     n_heads, n, _ = q_lat.shape
     _need(q_lat, "q_lat", torch.float32, (n_heads, n, kv_rank))
     _need(q, "q", k_pages.dtype, (n, n_heads, None))
@@ -1449,10 +1450,14 @@ def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, to
     if rot:
         _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
     _need(o_lat, "o_lat", k_pages.dtype, (n_heads, n, kv_rank))
+    part = None
+    if n_splits > 1:   # each split's (max, sum, weighted sum), joined by a second launch
+        part = torch.empty(n * n_heads * n_splits * (kv_rank + 2), dtype=torch.float32, device=o_lat.device)
     _ok(latent_attn_lib().dryft_latent_attn_rows(_act(k_pages, "k_pages"), _ptr(q_lat), _ptr(q), q.shape[2], int(q_rot_off), _ptr(k_pages),
                                                  _ptr(page_table), page_table.shape[1], k_pages.shape[2], _ptr(tok_slot), _ptr(tok_pos),
-                                                 _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(o_lat), n, n_heads, kv_rank, rot, float(scale),
-                                                 int(window or 0), _stream()), f"latent_attn_rows (rank {kv_rank}, rotated {rot})")
+                                                 _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(o_lat), _ptr(part), int(n_splits),
+                                                 n, n_heads, kv_rank, rot, float(scale), int(window or 0), _stream()),
+        f"latent_attn_rows (rank {kv_rank}, rotated {rot})", n_kernels=2 if n_splits > 1 else 1)
 
 
 def head_gate(o, gate, gate_col: int, out) -> None:

@@ -112,11 +112,21 @@ class LatentAttention:
         o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
         K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
                            self.position.interleaved, o_lat, kr, r, self.scale, self.window,
-                           inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
+                           inv_freq_lo=getattr(self.position, "inv_freq_lo", None), n_splits=self._n_splits(n, ctx.max_kv))
         o = self._per_head(o_lat, self.w_uv.transpose(1, 2), self.w_uv)
         out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
         K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)
         return linear(out, self.w_o, self.rt)
+
+    HEADS_PER_BLOCK, KEYS_PER_TILE = 8, 32     # csrc/latent_attn.cu
+
+    def _n_splits(self, n_rows: int, max_kv: int) -> int:
+        """Blocks that share a token's visible keys: enough to fill the device when the step has few tokens, a tile of keys
+        per block at least and 32 splits at most.  (A prompt step has a block per token and group of heads already.)"""
+        span = max(1, min(max_kv, self.window) if self.window else max_kv)
+        tiles = (span + self.KEYS_PER_TILE - 1) // self.KEYS_PER_TILE + 1
+        blocks = n_rows * ((self.n_heads + self.HEADS_PER_BLOCK - 1) // self.HEADS_PER_BLOCK)
+        return max(1, min(32, tiles, (2 * self.rt.sm_count) // max(1, blocks)))
 
     def _per_head(self, a: torch.Tensor, w_kn: torch.Tensor, w_nk: torch.Tensor) -> torch.Tensor:
         """``a[h] @ w[h]`` for every head, as float32 ``[H, n, m]``.  ``a [H, n, k]`` (any strides with unit stride along k),

@@ -177,6 +177,11 @@ def test_latent_attention_one_key_stands_out_at_every_edge(dtype, kv_rank, rot, 
         o_lat = torch.empty(H, len(ends), kv_rank, device=DEV, dtype=dtype)
         K.latent_attn_rows(q_lat, q, 5, k_pages, table, i32([1] * len(ends)), i32(ends), inv, interleaved, o_lat, kv_rank, rot, 1.3,
                            window or None)
+        for n_splits in (2, 5):    # the keys of every query shared by several blocks: the same result
+            split = torch.empty_like(o_lat)
+            K.latent_attn_rows(q_lat, q, 5, k_pages, table, i32([1] * len(ends)), i32(ends), inv, interleaved, split, kv_rank, rot, 1.3,
+                               window or None, n_splits=n_splits)
+            assert torch.allclose(split.float(), o_lat.float(), atol=1e-5 if dtype == torch.float32 else 1e-2), (mark, n_splits)
         # plain: the same scores in float64
         c, kr = r[:, :kv_rank].double().cpu(), r[:, kv_rank:].double().cpu()
         for e_i, e in enumerate(ends):
