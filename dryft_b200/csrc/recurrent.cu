@@ -18,7 +18,8 @@
 //                        b_t  = sqrt(1 - a_t^2) * i_t * u_t          (1 - a^2 as -expm1(2 log a): no cancellation)
 //                    leaves a_t and b_t [tokens, C] in 32-bit.
 // rglru_scan         S_t = a_t * S_(t-1) + b_t per channel, out_t = T( S_t * gelu_tanh(yproj_t + y_bias) ), then the new
-//                    state and the new tail (the last taps-1 inputs) are stored.
+//                    state and the new tail (the last taps-1 inputs) are stored.  Time is walked by eight warps at once,
+//                    each folding its own steps first (see the kernel).
 //
 // Everything that enters a recurrence is 32-bit whatever the activation type T.  Sizes are runtime arguments of any value
 // (shared memory permitting).  No block waits on another.
@@ -450,38 +451,60 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// A block takes 32 channels (a lane each) of one sequence and walks time in pieces of SCAN_WARPS * SCAN_SEG steps: every
+// warp folds its own SCAN_SEG steps into one (A, B) pair  S_out = A * S_in + B,  the pairs of the warps before it give its
+// S_in, and it walks its steps again for the outputs -- 2 * SCAN_SEG + SCAN_WARPS dependent steps a piece instead of
+// SCAN_WARPS * SCAN_SEG, with every warp's loads in flight at once.
+constexpr int SCAN_WARPS = 8, SCAN_SEG = 16;
+
 template <typename T>
-__global__ void rglru_scan_kernel(const T* __restrict__ proj, int ld, int y_off, const float* __restrict__ y_bias, int x_off,
-                                  const float* __restrict__ x_bias, const int* __restrict__ cu_q,
-                                  const int* __restrict__ seq_slot, const float* __restrict__ a_in,
-                                  const float* __restrict__ b_in, float* __restrict__ state, float* __restrict__ tail, int taps,
-                                  T* __restrict__ out, int C) {
+__global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_kernel(
+    const T* __restrict__ proj, int ld, int y_off, const float* __restrict__ y_bias, int x_off,
+    const float* __restrict__ x_bias, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+    const float* __restrict__ a_in, const float* __restrict__ b_in, float* __restrict__ state, float* __restrict__ tail,
+    int taps, T* __restrict__ out, int C) {
+  __shared__ float As[SCAN_WARPS][32], Bs[SCAN_WARPS][32], carry[32];
   const int b = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.y * 32 + lane;
   const int slot = seq_slot[b];
-  if (slot < 0 || c >= C) return;
+  if (slot < 0) return;
+  const bool on = c < C;
   const int n0 = cu_q[b], n1 = cu_q[b + 1];
-  float S = state[(size_t)slot * C + c];
-  const float yb = y_bias[c];
-  for (int nb = n0; nb < n1; nb += 8) {   // eight tokens' inputs asked for at once, then folded in order
-    float av[8], bv[8], yv[8];
+  if (warp == 0) carry[lane] = on ? state[(size_t)slot * C + c] : 0.f;
+  const float yb = on ? y_bias[c] : 0.f;
+  __syncthreads();
+  for (int t0 = n0; t0 < n1; t0 += SCAN_WARPS * SCAN_SEG) {
+    const int first = t0 + warp * SCAN_SEG;
+    float av[SCAN_SEG], bv[SCAN_SEG], yv[SCAN_SEG];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (nb + u < n1) {
-        av[u] = a_in[(size_t)(nb + u) * C + c];
-        bv[u] = b_in[(size_t)(nb + u) * C + c];
-        yv[u] = to_f32<T>(proj[(size_t)(nb + u) * ld + y_off + c]);
-      }
+    for (int i = 0; i < SCAN_SEG; ++i) {
+      const int n = first + i;
+      const bool ok = on && n < n1;
+      av[i] = ok ? a_in[(size_t)n * C + c] : 1.f;      // steps behind the end change nothing
+      bv[i] = ok ? b_in[(size_t)n * C + c] : 0.f;
+      yv[i] = ok ? to_f32<T>(proj[(size_t)n * ld + y_off + c]) : 0.f;
     }
+    float A = 1.f, B = 0.f;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (nb + u < n1) {
-        S = fmaf(av[u], S, bv[u]);
-        out[(size_t)(nb + u) * C + c] = from_f32<T>(S * gelu_tanh_f(yv[u] + yb));
-      }
+    for (int i = 0; i < SCAN_SEG; ++i) { B = fmaf(av[i], B, bv[i]); A *= av[i]; }
+    As[warp][lane] = A;
+    Bs[warp][lane] = B;
+    __syncthreads();
+    float S = carry[lane];
+    for (int w = 0; w < warp; ++w) S = fmaf(As[w][lane], S, Bs[w][lane]);
+#pragma unroll
+    for (int i = 0; i < SCAN_SEG; ++i) {
+      const int n = first + i;
+      S = fmaf(av[i], S, bv[i]);
+      if (on && n < n1) out[(size_t)n * C + c] = from_f32<T>(S * gelu_tanh_f(yv[i] + yb));
     }
+    __syncthreads();          // every warp has read the carry
+    if (warp == SCAN_WARPS - 1) carry[lane] = S;
+    __syncthreads();
   }
-  state[(size_t)slot * C + c] = S;
+  if (warp != 0 || !on) return;
+  state[(size_t)slot * C + c] = carry[lane];
   const int K1 = taps - 1, q = n1 - n0;
   const float xb = x_bias[c];
   for (int j = 0; j < K1; ++j) {   // ascending: an old entry is read before the entry below it is overwritten
@@ -598,8 +621,8 @@ DRYFT_API int dryft_rglru_scan(int is_bf16, const void* proj, int ld, int y_off,
                                float* state, float* tail, int taps, void* out, int n_seqs, int C, cudaStream_t st) {
   if (n_seqs <= 0) return 0;
   typedef __nv_bfloat16 bf;
-  const int threads = 128;
-  dim3 grid(n_seqs, (C + threads - 1) / threads);
+  const int threads = SCAN_WARPS * 32;
+  dim3 grid(n_seqs, (C + 31) / 32);
   if (grid.y > 65535) return DRYFT_ERR_UNSUPPORTED;
   if (is_bf16)
     rglru_scan_kernel<bf><<<grid, threads, 0, st>>>((const bf*)proj, ld, y_off, y_bias, x_off, x_bias, cu_q, seq_slot, a_in, b_in, state,
