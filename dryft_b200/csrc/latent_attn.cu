@@ -8,7 +8,7 @@
 //                      cq = T( rmsnorm(dq) * w_q )                        -> the query up-projection's input
 //                      c  = rmsnorm(dkv[:kv_rank]) * w_kv ; k_rot = rotate(dkv[kv_rank:]) at the token's position
 //                      cache row (slot, position) <- T([c | k_rot])
-// latent_attn_rows   one block per (query token, group of heads, split of the keys), a warp per head.  Keys
+// latent_attn_rows   one block per (query token, group of 16 heads, split of the keys), four heads a warp.  Keys
 //                    position-window+1 .. position (all keys from 0 if window is 0) are staged 32 at a time in shared memory
 //                    as floats (16-byte loads, several in flight per thread); a lane takes a key for the scores (softmax
 //                    running maximum and sum in 32-bit) and a slice of the latent for the weighted sum.  A step of few
@@ -25,7 +25,9 @@
 
 namespace {
 constexpr int PREP_THREADS = 256;
-constexpr int HPB = 8;         // heads (warps) per block of latent_attn_rows
+constexpr int HW = 4;          // heads a warp of latent_attn_rows
+constexpr int WPB = 4;         // warps a block
+constexpr int HPB = HW * WPB;  // heads a block
 constexpr int KT = 32;         // keys per staged tile
 
 // sin and cos of  pos * (f_hi + f_lo)  for a rotary position: the product is formed in 32-bit, and what its rounding
@@ -88,6 +90,14 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
     dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
 }
 
+// Floats per staged key row: a multiple of four (16-byte reads) whose quarter is odd, so that the rows of a warp's 32
+// keys fall on different banks.
+__host__ __device__ __forceinline__ int tile_row(int Dk) {
+  int d = (Dk + 3) & ~3;
+  if (((d >> 2) & 1) == 0) d += 4;
+  return d;
+}
+
 // 16 bytes of a cached row as floats (8 bfloat16 or 4 float)
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
@@ -105,23 +115,25 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
-// One block per (query token, group of HPB heads, split of the visible keys).  With one split the result goes to o_lat;
-// with several, each block leaves (max, sum, unnormalised weighted sum) in `part` and latent_combine joins them.
+// One block per (query token, group of HPB heads, split of the visible keys); a warp takes HW heads, so that a key's
+// staged row is read from shared memory once for all of them (16 bytes at a time where the row length allows): the loop is
+// bound by shared-memory reads, and this quarters them.  With one split the result goes to o_lat; with several, each block
+// leaves (max, sum, unnormalised weighted sum) in `part` and latent_combine joins them.
 template <typename T, int NR>
-__global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
+__global__ void __launch_bounds__(WPB * 32) latent_attn_rows_kernel(
     const float* __restrict__ q_lat, const T* __restrict__ q, int q_stride, int q_rot_off, const T* __restrict__ k_pages,
     const int* __restrict__ page_table, int max_pages, int page_size, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
     int interleaved, T* __restrict__ o_lat, float* __restrict__ part, int n_splits, int n_tokens, int H, int kv_rank, int rot,
     float scale, int window) {
   extern __shared__ __align__(16) float sm[];
-  const int Dk = kv_rank + rot, Dp = Dk + 1;
+  const int Dk = kv_rank + rot, Dq = (Dk + 3) & ~3, Dp = tile_row(Dk);
   float* tile = sm;                                  // [KT][Dp]
-  float* qs_all = tile + (size_t)KT * Dp;            // [HPB][Dk]
-  float* raw = qs_all + (size_t)HPB * Dk;            // [HPB][rot]
+  float* qs_all = tile + (size_t)KT * Dp;            // [HPB][Dq]
+  float* raw = qs_all + (size_t)HPB * Dq;            // [HPB][rot]
   const int n = blockIdx.x, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hd = blockIdx.y * HPB + warp;
+  const int hd0 = blockIdx.y * HPB + warp * HW;      // this warp's first head
   const int slot = tok_slot[n];
   if (slot < 0) return;
   const int pos = tok_pos[n];
@@ -131,24 +143,34 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
   const int per_split = (tiles_all + n_splits - 1) / n_splits;
   const int lo = lo_all + split * per_split * KT;
   const int hi = min(pos, lo + per_split * KT - 1);   // last key of this split
-  const bool live = hd < H;
-  float* qs = qs_all + (size_t)warp * Dk;
-  if (live) {
-    const float* ql = q_lat + ((size_t)hd * n_tokens + n) * kv_rank;
-    for (int d = lane; d < kv_rank; d += 32) qs[d] = ql[d] * scale;
-    const T* qr = q + ((size_t)n * H + hd) * q_stride + q_rot_off;
-    float* rw = raw + (size_t)warp * rot;
+  const int nh = max(0, min(HW, H - hd0));            // live heads of this warp
+  float* qs = qs_all + (size_t)warp * HW * Dq;
+  for (int i = 0; i < HW; ++i) {
+    float* qi = qs + (size_t)i * Dq;
+    if (i >= nh) {   // a head that does not exist: zeros, so that its sums stay finite
+      for (int d = lane; d < Dq; d += 32) qi[d] = 0.f;
+      continue;
+    }
+    const float* ql = q_lat + ((size_t)(hd0 + i) * n_tokens + n) * kv_rank;
+    for (int d = lane; d < kv_rank; d += 32) qi[d] = ql[d] * scale;
+    const T* qr = q + ((size_t)n * H + hd0 + i) * q_stride + q_rot_off;
+    float* rw = raw + (size_t)(warp * HW + i) * rot;
     for (int d = lane; d < rot; d += 32) rw[d] = to_f32<T>(qr[d]);
     __syncwarp();
-    for (int d = lane; d < rot; d += 32) qs[kv_rank + d] = rotated(rw, d, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo) * scale;
+    for (int d = lane; d < rot; d += 32) qi[kv_rank + d] = rotated(rw, d, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo) * scale;
+    for (int d = Dk + lane; d < Dq; d += 32) qi[d] = 0.f;
   }
-  float m = -INFINITY, l = 0.f;
-  float acc[NR];
+  float m[HW], l[HW], acc[HW][NR];
 #pragma unroll
-  for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+  for (int i = 0; i < HW; ++i) {
+    m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[i][r] = 0.f;
+  }
   const int* pt = page_table + (size_t)slot * max_pages;
   constexpr int VN = Vec16<T>::N;
   const bool vec_ok = (Dk % VN) == 0;     // rows start on 16-byte boundaries
+  const bool quad_ok = (Dk & 3) == 0;     // 16-byte reads of the staged rows
   const int vpr = Dk / VN;
   for (int j0 = lo; j0 <= hi; j0 += KT) {
     const int cnt = min(KT, hi - j0 + 1);
@@ -156,12 +178,12 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
     if (vec_ok) {
       // every thread asks for four 16-byte pieces before it unpacks the first: the loads' round trips overlap
       const int total = cnt * vpr;
-      for (int base = threadIdx.x; base < total; base += 4 * HPB * 32) {
+      for (int base = threadIdx.x; base < total; base += 4 * WPB * 32) {
         uint4 v[4];
         int at[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int idx = base + u * HPB * 32;
+          const int idx = base + u * WPB * 32;
           at[u] = -1;
           if (idx < total) {
             const int kk = idx / vpr, c = idx - kk * vpr, j = j0 + kk;
@@ -176,65 +198,90 @@ __global__ void __launch_bounds__(HPB * 32) latent_attn_rows_kernel(
             float f[VN];
             Vec16<T>::unpack(v[u], f);
 #pragma unroll
-            for (int e = 0; e < VN; ++e) tile[at[u] + e] = f[e];
+            for (int e = 0; e < VN; e += 4) *reinterpret_cast<float4*>(tile + at[u] + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
           }
         }
       }
     } else {
-      for (int kk = warp; kk < cnt; kk += HPB) {
+      for (int kk = warp; kk < cnt; kk += WPB) {
         const int j = j0 + kk;
         const T* src = k_pages + ((size_t)pt[j / page_size] * page_size + j % page_size) * Dk;
         for (int d = lane; d < Dk; d += 32) tile[kk * Dp + d] = to_f32<T>(src[d]);
       }
     }
     __syncthreads();
-    if (!live) continue;
-    float s = -INFINITY;
+    if (nh == 0) continue;
+    float s[HW];
+#pragma unroll
+    for (int i = 0; i < HW; ++i) s[i] = 0.f;
     if (lane < cnt) {
       const float* kr = tile + lane * Dp;
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;   // four chains instead of one
-      int d = 0;
-      for (; d + 3 < Dk; d += 4) {
-        a0 = fmaf(qs[d], kr[d], a0); a1 = fmaf(qs[d + 1], kr[d + 1], a1);
-        a2 = fmaf(qs[d + 2], kr[d + 2], a2); a3 = fmaf(qs[d + 3], kr[d + 3], a3);
-      }
-      for (; d < Dk; ++d) a0 = fmaf(qs[d], kr[d], a0);
-      s = (a0 + a1) + (a2 + a3);
-    }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float p = lane < cnt ? expf(s - m_new) : 0.f;
-    const float corr = expf(m - m_new);   // 0 the first time (m = -inf)
-    l = l * corr + warp_sum(p);
+      if (quad_ok) {
+        for (int d = 0; d < Dk; d += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
-    for (int r = 0; r < NR; ++r) acc[r] *= corr;
+          for (int i = 0; i < HW; ++i) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + (size_t)i * Dq + d);
+            s[i] = fmaf(q4.x, k4.x, fmaf(q4.y, k4.y, fmaf(q4.z, k4.z, fmaf(q4.w, k4.w, s[i]))));
+          }
+        }
+      } else {
+        for (int d = 0; d < Dk; ++d) {
+          const float kv = kr[d];
+#pragma unroll
+          for (int i = 0; i < HW; ++i) s[i] = fmaf(qs[(size_t)i * Dq + d], kv, s[i]);
+        }
+      }
+    }
+    float p[HW];
+#pragma unroll
+    for (int i = 0; i < HW; ++i) {
+      const float si = lane < cnt ? s[i] : -INFINITY;
+      const float m_new = fmaxf(m[i], warp_max(si));
+      p[i] = lane < cnt ? expf(si - m_new) : 0.f;
+      const float corr = expf(m[i] - m_new);   // 0 the first time (m = -inf)
+      l[i] = l[i] * corr + warp_sum(p[i]);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) acc[i][r] *= corr;
+      m[i] = m_new;
+    }
     for (int kk = 0; kk < cnt; ++kk) {
-      const float pk = __shfl_sync(0xffffffffu, p, kk);
       const float* kr = tile + kk * Dp;
+      float cv[NR];
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
         const int d = lane + 32 * r;
-        if (d < kv_rank) acc[r] = fmaf(pk, kr[d], acc[r]);
+        cv[r] = d < kv_rank ? kr[d] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < HW; ++i) {
+        const float pk = __shfl_sync(0xffffffffu, p[i], kk);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) acc[i][r] = fmaf(pk, cv[r], acc[i][r]);
       }
     }
-    m = m_new;
   }
-  if (!live) return;
-  if (n_splits > 1) {   // a split without keys leaves max = -inf, sum = 0
-    float* dst = part + (((size_t)n * H + hd) * n_splits + split) * (kv_rank + 2);
-    if (lane == 0) { dst[0] = m; dst[1] = l; }
 #pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const int d = lane + 32 * r;
-      if (d < kv_rank) dst[2 + d] = acc[r];
+  for (int i = 0; i < HW; ++i) {
+    if (i >= nh) break;
+    const int hd = hd0 + i;
+    if (n_splits > 1) {   // a split without keys leaves max = -inf, sum = 0
+      float* dst = part + (((size_t)n * H + hd) * n_splits + split) * (kv_rank + 2);
+      if (lane == 0) { dst[0] = m[i]; dst[1] = l[i]; }
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < kv_rank) dst[2 + d] = acc[i][r];
+      }
+    } else {
+      T* dst = o_lat + ((size_t)hd * n_tokens + n) * kv_rank;
+      const float inv = 1.f / l[i];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < kv_rank) dst[d] = from_f32<T>(acc[i][r] * inv);
+      }
     }
-    return;
-  }
-  T* dst = o_lat + ((size_t)hd * n_tokens + n) * kv_rank;
-  const float inv = 1.f / l;
-#pragma unroll
-  for (int r = 0; r < NR; ++r) {
-    const int d = lane + 32 * r;
-    if (d < kv_rank) dst[d] = from_f32<T>(acc[r] * inv);
   }
 }
 
@@ -294,11 +341,11 @@ int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, 
                 const float* inv_freq_lo, int interleaved, void* o_lat, float* part, int n_splits, int n_tokens, int H, int kv_rank,
                 int rot, float scale, int window, cudaStream_t st) {
   const int Dk = kv_rank + rot;
-  const size_t smem = sizeof(float) * ((size_t)KT * (Dk + 1) + (size_t)HPB * Dk + (size_t)HPB * rot);
+  const size_t smem = sizeof(float) * ((size_t)KT * tile_row(Dk) + (size_t)HPB * ((Dk + 3) & ~3) + (size_t)HPB * rot);
   int rc = opt_in(latent_attn_rows_kernel<T, NR>, smem);
   if (rc) return rc;
   dim3 grid(n_tokens, (H + HPB - 1) / HPB, n_splits);
-  latent_attn_rows_kernel<T, NR><<<grid, HPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
+  latent_attn_rows_kernel<T, NR><<<grid, WPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
                                                                max_pages, page_size, tok_slot, tok_pos, inv_freq, inv_freq_lo,
                                                                interleaved, (T*)o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale,
                                                                window);

@@ -118,7 +118,7 @@ class LatentAttention:
         K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)
         return linear(out, self.w_o, self.rt)
 
-    HEADS_PER_BLOCK, KEYS_PER_TILE = 8, 32     # csrc/latent_attn.cu
+    HEADS_PER_BLOCK, KEYS_PER_TILE = 16, 32     # csrc/latent_attn.cu
 
     def _n_splits(self, n_rows: int, max_kv: int) -> int:
         """Blocks that share a token's visible keys: enough to fill the device when the step has few tokens, a tile of keys
