@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
     int rot, const float* __restrict__ w_kv, float eps, const float* __restrict__ inv_freq,
     const float* __restrict__ inv_freq_lo, int interleaved, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, T* __restrict__ cq, T* __restrict__ k_pages,
-    const int* __restrict__ page_table, int max_pages, int page_size) {
+    const int* __restrict__ page_table, int max_pages, int page_size, T* __restrict__ c_out) {
   extern __shared__ __align__(16) float buf[];   // [rot]
   __shared__ float scratch[33];
   const int n = blockIdx.x;
@@ -85,7 +85,11 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prep_kernel(
   for (int c = threadIdx.x; c < rot; c += PREP_THREADS) buf[c] = to_f32<T>(row[dkv_off + kv_rank + c]);
   ss = block_sum(ss, scratch);   // also orders buf
   const float inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
-  for (int c = threadIdx.x; c < kv_rank; c += PREP_THREADS) dst[c] = from_f32<T>(to_f32<T>(row[dkv_off + c]) * inv * w_kv[c]);
+  for (int c = threadIdx.x; c < kv_rank; c += PREP_THREADS) {
+    const T v = from_f32<T>(to_f32<T>(row[dkv_off + c]) * inv * w_kv[c]);
+    dst[c] = v;
+    if (c_out) c_out[(size_t)n * kv_rank + c] = v;   // the latent as rows too, for a step that makes keys and values from it
+  }
   for (int c = threadIdx.x; c < rot; c += PREP_THREADS)
     dst[kv_rank + c] = from_f32<T>(rotated(buf, c, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
 }
@@ -326,6 +330,75 @@ __global__ void head_gate_kernel(const float* __restrict__ o, const T* __restric
   out[i] = from_f32<T>(val);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// A step in which every sequence starts at position 0 holds all its keys itself: the per-head keys and values are then made
+// from the step's latents by one matrix product and handed, in pages of the step's own, to the library's tensor-core prompt
+// attention (the ordinary kind: per-head keys [unrotated | rotated part] and values).
+//
+// latent_scratch_table   table[slot_b][p] = (pages of the sequences before b) + p   for the step's sequences
+// latent_expand_store    per token: q_out[n, h] = [q_plain | rotate(q_rot)], key page row = [k_plain,h | rotate(k_rot)],
+//                        value page row = [v_h | zeros]  (all of the head size `hd` >= the value size)
+// head_gate_rows         out[n, h*V + v] = T( o[n, h, v] * sigmoid(gate_logit[n, h]) )   for o [n, H, hd]
+__global__ void latent_scratch_table_kernel(const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int n_seqs,
+                                            int* __restrict__ table, int max_pages, int page_size) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n_seqs) return;
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  int base = 0;
+  for (int bb = 0; bb < b; ++bb) base += (cu_q[bb + 1] - cu_q[bb] + page_size - 1) / page_size;
+  const int np = (cu_q[b + 1] - cu_q[b] + page_size - 1) / page_size;
+  for (int p = 0; p < np && p < max_pages; ++p) table[(size_t)slot * max_pages + p] = base + p;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_THREADS) latent_expand_store_kernel(
+    const T* __restrict__ q, const T* __restrict__ kv, int kv_ld, int v_off, const T* __restrict__ proj, int ld, int krot_off,
+    const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, int interleaved,
+    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ table, int max_pages,
+    int page_size, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int H, int dim, int rot, int vdim) {
+  extern __shared__ __align__(16) float buf[];   // [rot] the shared key part, rotated; then [H][rot] raw query parts
+  const int n = blockIdx.x;
+  const int slot = tok_slot[n];
+  if (slot < 0) return;
+  const int pos = tok_pos[n], hd = dim + rot;
+  float* krot = buf;
+  float* qraw = buf + rot;
+  for (int c = threadIdx.x; c < rot; c += PREP_THREADS) krot[c] = to_f32<T>(proj[(size_t)n * ld + krot_off + c]);
+  for (int i = threadIdx.x; i < H * rot; i += PREP_THREADS)
+    qraw[i] = to_f32<T>(q[((size_t)n * H + i / rot) * hd + dim + i % rot]);
+  __syncthreads();
+  const size_t page = (size_t)table[(size_t)slot * max_pages + pos / page_size];
+  for (int i = threadIdx.x; i < H * hd; i += PREP_THREADS) {
+    const int h = i / hd, d = i % hd;
+    const size_t at = ((page * H + h) * page_size + pos % page_size) * hd + d;
+    T qv, kvv;
+    if (d < dim) {
+      qv = q[((size_t)n * H + h) * hd + d];
+      kvv = kv[(size_t)n * kv_ld + h * dim + d];
+    } else {
+      qv = from_f32<T>(rotated(qraw + h * rot, d - dim, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
+      kvv = from_f32<T>(rotated(krot, d - dim, rot, interleaved != 0, (float)pos, inv_freq, inv_freq_lo));
+    }
+    q_out[((size_t)n * H + h) * hd + d] = qv;
+    k_pages[at] = kvv;
+    v_pages[at] = d < vdim ? kv[(size_t)n * kv_ld + v_off + h * vdim + d] : from_f32<T>(0.f);
+  }
+}
+
+template <typename T>
+__global__ void head_gate_rows_kernel(const T* __restrict__ o, int hd, const T* __restrict__ gate, int gate_ld,
+                                      T* __restrict__ out, int n_tokens, int H, int vdim) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * H * vdim) return;
+  const int v = (int)(i % vdim);
+  const int h = (int)((i / vdim) % H);
+  const size_t n = i / ((size_t)vdim * H);
+  float val = to_f32<T>(o[(n * H + h) * hd + v]);
+  if (gate) val *= 1.f / (1.f + expf(-to_f32<T>(gate[n * gate_ld + h])));
+  out[i] = from_f32<T>(val);
+}
+
 template <typename K> int opt_in(K kernel, size_t bytes) {
   if (bytes > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (bytes > 48 * 1024) {
@@ -358,8 +431,9 @@ int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, 
 
 DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_off, int q_rank, const float* w_q, int dkv_off,
                                 int kv_rank, int rot, const float* w_kv, float eps, const float* inv_freq,
-                                const float* inv_freq_lo, int interleaved, const int* tok_slot, const int* tok_pos, void* cq, void* k_pages, const int* page_table,
-                                int max_pages, int page_size, int n, cudaStream_t st) {
+                                const float* inv_freq_lo, int interleaved, const int* tok_slot, const int* tok_pos, void* cq,
+                                void* k_pages, const int* page_table, int max_pages, int page_size, void* c_out, int n,
+                                cudaStream_t st) {
   if (n <= 0) return 0;
   if (kv_rank <= 0 || rot < 0 || (rot & 1)) return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
@@ -368,11 +442,11 @@ DRYFT_API int dryft_latent_prep(int is_bf16, const void* proj, int ld, int dq_of
   if (is_bf16)
     latent_prep_kernel<bf><<<n, PREP_THREADS, smem, st>>>((const bf*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv, eps,
                                                           inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos, (bf*)cq, (bf*)k_pages, page_table,
-                                                          max_pages, page_size);
+                                                          max_pages, page_size, (bf*)c_out);
   else
     latent_prep_kernel<float><<<n, PREP_THREADS, smem, st>>>((const float*)proj, ld, dq_off, q_rank, w_q, dkv_off, kv_rank, rot, w_kv,
                                                              eps, inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos, (float*)cq, (float*)k_pages,
-                                                             page_table, max_pages, page_size);
+                                                             page_table, max_pages, page_size, (float*)c_out);
   return launch_status();
 }
 
@@ -398,6 +472,46 @@ DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void
   if (nr <= 8) { DRYFT_LATENT_ROWS(8); }
   DRYFT_LATENT_ROWS(16);
 #undef DRYFT_LATENT_ROWS
+}
+
+DRYFT_API int dryft_latent_scratch_table(const int* cu_q, const int* seq_slot, int n_seqs, int* table, int max_pages, int page_size,
+                                         cudaStream_t st) {
+  if (n_seqs <= 0) return 0;
+  latent_scratch_table_kernel<<<(n_seqs + 127) / 128, 128, 0, st>>>(cu_q, seq_slot, n_seqs, table, max_pages, page_size);
+  return launch_status();
+}
+
+DRYFT_API int dryft_latent_expand_store(int is_bf16, const void* q, const void* kv, int kv_ld, int v_off, const void* proj, int ld,
+                                        int krot_off, const float* inv_freq, const float* inv_freq_lo, int interleaved,
+                                        const int* tok_slot, const int* tok_pos, const int* table, int max_pages, int page_size,
+                                        void* q_out, void* k_pages, void* v_pages, int n, int H, int dim, int rot, int vdim,
+                                        cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (H <= 0 || dim <= 0 || rot < 0 || (rot & 1) || vdim > dim + rot) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const size_t smem = sizeof(float) * ((size_t)rot * (H + 1) + 1);
+  if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  if (is_bf16)
+    latent_expand_store_kernel<bf><<<n, PREP_THREADS, smem, st>>>((const bf*)q, (const bf*)kv, kv_ld, v_off, (const bf*)proj, ld, krot_off,
+                                                                  inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos, table, max_pages,
+                                                                  page_size, (bf*)q_out, (bf*)k_pages, (bf*)v_pages, H, dim, rot, vdim);
+  else
+    latent_expand_store_kernel<float><<<n, PREP_THREADS, smem, st>>>((const float*)q, (const float*)kv, kv_ld, v_off, (const float*)proj,
+                                                                     ld, krot_off, inv_freq, inv_freq_lo, interleaved, tok_slot, tok_pos,
+                                                                     table, max_pages, page_size, (float*)q_out, (float*)k_pages,
+                                                                     (float*)v_pages, H, dim, rot, vdim);
+  return launch_status();
+}
+
+DRYFT_API int dryft_head_gate_rows(int is_bf16, const void* o, int hd, const void* gate, int gate_ld, void* out, int n_tokens, int H,
+                                   int vdim, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  typedef __nv_bfloat16 bf;
+  const size_t total = (size_t)n_tokens * H * vdim;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (is_bf16) head_gate_rows_kernel<bf><<<blocks, 256, 0, st>>>((const bf*)o, hd, (const bf*)gate, gate_ld, (bf*)out, n_tokens, H, vdim);
+  else head_gate_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)o, hd, (const float*)gate, gate_ld, (float*)out, n_tokens, H, vdim);
+  return launch_status();
 }
 
 DRYFT_API int dryft_head_gate(int is_bf16, const float* o, const void* gate, int gate_ld, void* out, int n_tokens, int H, int vdim,

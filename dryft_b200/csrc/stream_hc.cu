@@ -209,20 +209,29 @@ __global__ void __launch_bounds__(THREADS) hc_step_kernel(
   for (int c = threadIdx.x; c < width; c += THREADS) h[(size_t)r * width + c] = from_f32<T>(row[c] * inv * norm_w[c]);
 }
 
-template <typename T>
-__global__ void glu_clamp_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, float limit,
-                                 int has_limit, float alpha, float up_offset) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)rows * inter) return;
-  const size_t r = i / inter, f = i % inter;
-  float g = to_f32<T>(gate_up[r * 2 * inter + f]);
-  float u = to_f32<T>(gate_up[r * 2 * inter + inter + f]);
+__device__ __forceinline__ float glu_one(float g, float u, float limit, int has_limit, float alpha, float up_offset) {
   if (has_limit) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
   }
-  const float act = g / (1.f + expf(-alpha * g));
-  out[i] = from_f32<T>(act * (u + up_offset));
+  return g / (1.f + expf(-alpha * g)) * (u + up_offset);
+}
+
+// VEC = 4: four columns a thread (8- or 16-byte accesses; the width is then a multiple of four), VEC = 1: any width
+template <typename T, int VEC>
+__global__ void glu_clamp_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, float limit,
+                                 int has_limit, float alpha, float up_offset) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (i >= (size_t)rows * inter) return;
+  const size_t r = i / inter, f = i % inter;
+  const T* g = gate_up + r * 2 * inter + f;
+  if (VEC == 4) {
+    const float4 gv = load4<T>(g), uv = load4<T>(g + inter);
+    store4<T>(out + i, make_float4(glu_one(gv.x, uv.x, limit, has_limit, alpha, up_offset), glu_one(gv.y, uv.y, limit, has_limit, alpha, up_offset),
+                                   glu_one(gv.z, uv.z, limit, has_limit, alpha, up_offset), glu_one(gv.w, uv.w, limit, has_limit, alpha, up_offset)));
+  } else {
+    out[i] = from_f32<T>(glu_one(to_f32<T>(g[0]), to_f32<T>(g[inter]), limit, has_limit, alpha, up_offset));
+  }
 }
 
 template <typename K> int row_smem(K kernel, int width) {
@@ -287,11 +296,14 @@ DRYFT_API int dryft_glu_clamp(int is_bf16, const void* gate_up, void* out, int r
   if (rows <= 0 || inter <= 0) return 0;
   typedef __nv_bfloat16 bf;
   const size_t total = (size_t)rows * inter;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (is_bf16)
-    glu_clamp_kernel<bf><<<blocks, 256, 0, st>>>((const bf*)gate_up, (bf*)out, rows, inter, limit, has_limit, alpha, up_offset);
-  else
-    glu_clamp_kernel<float><<<blocks, 256, 0, st>>>((const float*)gate_up, (float*)out, rows, inter, limit, has_limit, alpha,
-                                                    up_offset);
+  if ((inter & 3) == 0) {
+    const unsigned blocks = (unsigned)((total / 4 + 255) / 256);
+    if (is_bf16) glu_clamp_kernel<bf, 4><<<blocks, 256, 0, st>>>((const bf*)gate_up, (bf*)out, rows, inter, limit, has_limit, alpha, up_offset);
+    else glu_clamp_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)gate_up, (float*)out, rows, inter, limit, has_limit, alpha, up_offset);
+  } else {
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (is_bf16) glu_clamp_kernel<bf, 1><<<blocks, 256, 0, st>>>((const bf*)gate_up, (bf*)out, rows, inter, limit, has_limit, alpha, up_offset);
+    else glu_clamp_kernel<float, 1><<<blocks, 256, 0, st>>>((const float*)gate_up, (float*)out, rows, inter, limit, has_limit, alpha, up_offset);
+  }
   return launch_status();
 }

@@ -39,6 +39,8 @@ class Stepper:
         # query tokens per prefill tile: the smallest any mixer asks for (64 unless every mixer takes more)
         self.prefill_tile = min([getattr(b.mixer, "prefill_tile", 64) for b in model.blocks] or [64])
         self.last_decode_slots: Optional[torch.Tensor] = None
+        # whether a step in which every sequence starts at position 0 is told apart (``StepContext.fresh``)
+        self.uses_fresh = any(getattr(b.mixer, "uses_fresh_steps", False) for b in model.blocks)
         self._prompt_graphs: Dict[tuple, "_PromptGraph"] = {}   # (tokens, sequences, wanted rows, tiles) -> captured step
         self._prompt_shapes_seen: set = set()
 
@@ -99,6 +101,8 @@ class Stepper:
         max_kv = max(st + q for st, q in zip(starts, q_lens))
         logits = None
         shape = (N, B, W, T)
+        if self.uses_fresh:   # a mixer takes another path when no key is older than the step: the launches differ
+            shape += (not decode and all(st == 0 for st in starts),)
         if self.cuda_graphs and not decode and N >= self.PROMPT_GRAPH_MIN_TOKENS:
             # A prompt step's launches depend on these four counts only (every length, position, slot and tile is
             # data the kernels read on the device), so a step of a shape seen before is replayed from a captured
@@ -134,7 +138,8 @@ class Stepper:
 
     def _run(self, dev: torch.Tensor, meta: torch.Tensor, shape, decode: bool, max_kv: int) -> Optional[torch.Tensor]:
         """The device side of a step: ``dev`` holds the step's integers as ``step`` packs them."""
-        N, B, W, T = shape
+        N, B, W, T = shape[:4]
+        fresh = bool(shape[4]) if len(shape) > 4 else False
         o = 0
         d_tokens = dev[o:o + N]; o += N
         d_cu = dev[o:o + B + 1]; o += B + 1
@@ -145,7 +150,7 @@ class Stepper:
         tok_slot, tok_pos = meta[:N], meta[N:]
         K.step_meta(d_cu, d_slot, self.cache.seq_len, tok_slot, tok_pos, N, B)
         ctx = StepContext(n_tokens=N, n_seqs=B, tokens=d_tokens, cu_q=d_cu, seq_slot=d_slot, tok_slot=tok_slot,
-                          tok_pos=tok_pos, decode=decode, max_kv=max_kv,
+                          tok_pos=tok_pos, decode=decode, max_kv=max_kv, fresh=fresh,
                           tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None, n_tiles=T, tile_size=self.prefill_tile)
         logits = self.model.forward(ctx, self.cache, d_rows if W else None, W)
         K.step_advance(d_cu, d_slot, self.cache.seq_len, B)
@@ -195,7 +200,8 @@ class Stepper:
 
 
 class _PromptGraph:
-    """A captured prompt step of one shape: its own copy of the step's integers, its token metadata and the graph.
+    """A captured prompt step of one shape (its counts and, for models that tell such steps apart, whether every sequence
+    starts at position 0): its own copy of the step's integers, its token metadata and the graph.
     The reference captures decode steps only (``engine/dryft_qwen3/graphs.py:25-59``); its prompts run eagerly."""
 
     def __init__(self, stepper: Stepper, shape, n_ints: int):

@@ -1229,7 +1229,10 @@ def recurrent_lib() -> ctypes.CDLL:
 def latent_attn_lib() -> ctypes.CDLL:
     """Attention over cached low-rank latents."""
     return _single_lib("latent_attn", {
-        "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+        "dryft_latent_prep": [_i, _p, _i, _i, _i, _p, _i, _i, _i, _p, _f, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _p, _i, _p],
+        "dryft_latent_scratch_table": [_p, _p, _i, _p, _i, _i, _p],
+        "dryft_latent_expand_store": [_i, _p, _p, _i, _i, _p, _i, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p],
+        "dryft_head_gate_rows": [_i, _p, _i, _p, _i, _p, _i, _i, _i, _p],
         "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
         "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
     })
@@ -1412,7 +1415,7 @@ def rglru(proj, y_off: int, x_off: int, y_bias, x_bias, cu_q, seq_slot, tok_slot
 
 # ----------------------------------------------------------------------------- attention over cached latents
 def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int, rot: int, w_kv, eps: float, inv_freq,
-                interleaved: bool, tok_slot, tok_pos, cq, k_pages, page_table, inv_freq_lo=None) -> None:
+                interleaved: bool, tok_slot, tok_pos, cq, k_pages, page_table, inv_freq_lo=None, c_out=None) -> None:
     """Normalise the query latent into ``cq [n, q_rank]``; normalise the key/value latent, rotate the shared key part and
     write ``[c | k_rot]`` into the paged cache ``k_pages [pages, 1, page, kv_rank + rot]`` at each token's (slot, position)."""
     n, ld = proj.shape
@@ -1428,10 +1431,12 @@ def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int,
     _need(cq, "cq", proj.dtype, (n, q_rank))
     _need(k_pages, "k_pages", proj.dtype, (None, 1, None, kv_rank + rot))
     _need(page_table, "page_table", torch.int32)
+    if c_out is not None:   # the normalised key/value latent as rows too
+        _need(c_out, "c_out", proj.dtype, (n, kv_rank))
     _ok(latent_attn_lib().dryft_latent_prep(_act(proj, "proj"), _ptr(proj), ld, int(dq_off), q_rank, _ptr(w_q), int(dkv_off), kv_rank,
                                             rot, _ptr(w_kv), float(eps), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(tok_slot),
                                             _ptr(tok_pos), _ptr(cq), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
-                                            k_pages.shape[2], n, _stream()), "latent_prep")
+                                            k_pages.shape[2], _ptr(c_out), n, _stream()), "latent_prep")
 
 
 def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, tok_pos, inv_freq, interleaved: bool, o_lat,
@@ -1458,6 +1463,56 @@ def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, to
                                                  _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(o_lat), _ptr(part), int(n_splits),
                                                  n, n_heads, kv_rank, rot, float(scale), int(window or 0), _stream()),
         f"latent_attn_rows (rank {kv_rank}, rotated {rot})", n_kernels=2 if n_splits > 1 else 1)
+
+
+def latent_expand_store(q, kv, v_off: int, proj, krot_off: int, inv_freq, interleaved: bool, cu_q, seq_slot, n_seqs: int, tok_slot,
+                        tok_pos, table, q_out, k_pages, v_pages, dim: int, rot: int, vdim: int, inv_freq_lo=None) -> None:
+    """For a step whose sequences all start at position 0: pages of the step's own (``table [slots, pages]`` is filled
+    here) receive per-head keys ``[k_plain | rotated shared part]`` and values ``[v | zeros]`` of head size ``dim + rot``;
+    ``q_out [n, H, dim + rot]`` receives the queries with their rotated part rotated.  ``q [n, H, dim + rot]``,
+    ``kv [n, >= H*dim + H*vdim]`` (keys' unrotated parts at column 0, values at ``v_off``), ``proj`` holds the shared key part
+    at ``krot_off``.  Two launches."""
+    n, n_heads, hd = q.shape
+    _need(q, "q")
+    if hd != dim + rot or vdim > hd:
+        raise KernelError(f"latent_expand_store: head size {hd} against {dim} + {rot}, values of {vdim}")
+    _need(kv, "kv", q.dtype)
+    _need(proj, "proj", q.dtype)
+    if kv.dim() != 2 or kv.shape[0] < n or kv.shape[1] < max(n_heads * dim, v_off + n_heads * vdim) or krot_off + rot > proj.shape[1]:
+        raise KernelError("latent_expand_store: column ranges outside the rows")
+    page = k_pages.shape[2]
+    _need(q_out, "q_out", q.dtype, (n, n_heads, hd))
+    _need(k_pages, "k_pages", q.dtype, (None, n_heads, page, hd))
+    _need(v_pages, "v_pages", q.dtype, tuple(k_pages.shape))
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos"), (table, "table")):
+        _need(t, nm, torch.int32)
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    if k_pages.shape[0] < n // page + n_seqs or table.shape[1] < (n + page - 1) // page:
+        raise KernelError("latent_expand_store: too few pages for the step")
+    lib = latent_attn_lib()
+    _ok(lib.dryft_latent_scratch_table(_ptr(cu_q), _ptr(seq_slot), n_seqs, _ptr(table), table.shape[1], page, _stream()),
+        "latent_scratch_table")
+    _ok(lib.dryft_latent_expand_store(_act(q, "q"), _ptr(q), _ptr(kv), kv.shape[1], int(v_off), _ptr(proj), proj.shape[1], int(krot_off),
+                                      _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(tok_slot), _ptr(tok_pos),
+                                      _ptr(table), table.shape[1], page, _ptr(q_out), _ptr(k_pages), _ptr(v_pages), n, n_heads, dim, rot,
+                                      vdim, _stream()), "latent_expand_store")
+
+
+def head_gate_rows(o, gate, gate_col: int, out, n_heads: int, vdim: int) -> None:
+    """``out[n, h*V + v] = T(o[n, h*hd + v] * sigmoid(gate[n, gate_col + h]))`` for ``o [n, H*hd]`` (``gate`` None: no gate)."""
+    n = o.shape[0]
+    hd = o.shape[1] // n_heads
+    _need(o, "o", None, (n, n_heads * hd))
+    _need(out, "out", o.dtype, (n, n_heads * vdim))
+    gate_ptr, gate_ld = None, 0
+    if gate is not None:
+        _need(gate, "gate", out.dtype)
+        if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+            raise KernelError("head_gate_rows: gate columns outside the gate tensor")
+        gate_ptr, gate_ld = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    _ok(latent_attn_lib().dryft_head_gate_rows(_act(out, "out"), _ptr(o), hd, gate_ptr, gate_ld, _ptr(out), n, n_heads, vdim, _stream()),
+        "head_gate_rows")
 
 
 def head_gate(o, gate, gate_col: int, out) -> None:

@@ -82,6 +82,7 @@ class StepContext:
     tok_pos: torch.Tensor         # int32 [n_tokens]: absolute position of each token
     decode: bool                  # host: every sequence brings exactly one token
     max_kv: int = 0               # host: no sequence is longer than this after the step (a bound, may be loose)
+    fresh: bool = False           # host: every sequence of the step starts at position 0 (all its keys are in the step)
     tile_tok0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first packed token of a query tile
     tile_rows: Optional[torch.Tensor] = None   # int32 [n_tiles]: tokens in the tile (<= tile_size)
     n_tiles: int = 0

@@ -11,6 +11,9 @@ With ``H`` heads, per head ``d`` unrotated and ``r`` rotated query/key dims, val
 Only ``[c | k_rot]`` is cached, one row per token for all heads (a keys-only cache group).  The per-head key and value
 matrices are folded into the query and the output: ``q_lat = W_uk^T q_plain`` before attention, ``o = W_uv o_lat`` after,
 both as batched matrix products over the heads; attention itself runs over the cached rows (``csrc/latent_attn.cu``).
+A bfloat16 step in which every sequence starts at position 0 (all its keys are its own) makes per-head keys and values
+from its latents by one more product and runs the library's tensor-core prompt attention over pages of the step's own;
+every other step (a piece that continues a prompt, a single token, everything in 32-bit) runs over the cached latents.
 Norms, angles, scores, softmax and the weighted sum are 32-bit in both precisions.  ``W_dq | W_dkv | W_g`` are one
 product.  Every size and constant is a parameter; ``params["names"]`` maps the tensors' roles to their names.
 """
@@ -90,6 +93,14 @@ class LatentAttention:
         self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()        # [H, kr, d]: rows = outputs, for the 32-bit product
         self.w_uv = w_uv.reshape(H, dv, kr).contiguous()            # [H, dv, kr]: rows = outputs
         K.latent_attn_lib()
+        # prompts whose sequences all start at position 0 (bfloat16): keys and values per head from the step's own latents
+        # (one product), then the library's tensor-core prompt attention over pages of the step's own
+        hd = d + self.rot_dim
+        self.use_prompt_tc = rt.is_bf16 and hd % 16 == 0 and hd <= 256 and dv <= hd and rt.page_size == 64
+        self.uses_fresh_steps = self.use_prompt_tc
+        if self.use_prompt_tc:
+            self.w_ukv = torch.cat([w_uk, w_uv], dim=0).contiguous()      # [H*d + H*dv, kr]
+            K.attention_prefill_lib(hd, 1, rt.page_size)
 
     def kv_need(self) -> KVNeed:
         return KVNeed(1, self.kv_rank + self.rot_dim, self.window, values=False)
@@ -104,15 +115,33 @@ class LatentAttention:
         d, r, dv, kr = self.qk_dim, self.rot_dim, self.v_dim, self.kv_rank
         proj = linear(h, self.w_in, self.rt)
         cq = torch.empty((n, self.q_rank), dtype=h.dtype, device=dev)
+        lo = getattr(self.position, "inv_freq_lo", None)
+        fresh = self.use_prompt_tc and ctx.fresh and not ctx.decode and ctx.n_tiles > 0 and ctx.tile_size <= 64
+        c_rows = torch.empty((n, kr), dtype=h.dtype, device=dev) if fresh else None
         K.latent_prep(proj, 0, self.q_rank, self.dq_norm_w, self.dkv_off, kr, r, self.dkv_norm_w, self.eps, self.position.inv_freq,
-                      self.position.interleaved, ctx.tok_slot, ctx.tok_pos, cq, cache.k, cache.page_table,
-                      inv_freq_lo=getattr(self.position, "inv_freq_lo", None))
+                      self.position.interleaved, ctx.tok_slot, ctx.tok_pos, cq, cache.k, cache.page_table, inv_freq_lo=lo, c_out=c_rows)
         q = linear(cq, self.w_uq, self.rt).view(n, H, d + r)
+        if fresh:
+            page, hd = self.rt.page_size, d + r
+            kv = linear(c_rows, self.w_ukv, self.rt)                      # [n, H*d | H*dv]
+            n_pages = n // page + ctx.n_seqs + 1
+            k_s = torch.zeros((n_pages, H, page, hd), dtype=h.dtype, device=dev)
+            v_s = torch.zeros((n_pages, H, page, hd), dtype=h.dtype, device=dev)
+            table = torch.zeros((cache.page_table.shape[0], (n + page - 1) // page + 1), dtype=torch.int32, device=dev)
+            q_full = torch.empty((n, H, hd), dtype=h.dtype, device=dev)
+            K.latent_expand_store(q, kv, H * d, proj, self.dkv_off + kr, self.position.inv_freq, self.position.interleaved, ctx.cu_q,
+                                  ctx.seq_slot, ctx.n_seqs, ctx.tok_slot, ctx.tok_pos, table, q_full, k_s, v_s, d, r, dv, inv_freq_lo=lo)
+            o_pad = torch.empty((n, H * hd), dtype=h.dtype, device=dev)
+            K.attn_prefill(q_full, k_s, v_s, table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos, o_pad, ctx.n_tiles,
+                           self.scale, self.window)
+            out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
+            K.head_gate_rows(o_pad, proj if self.has_gate else None, self.gate_col, out, H, dv)
+            return linear(out, self.w_o, self.rt)
         q_lat = self._per_head(q[:, :, :d].transpose(0, 1), self.w_uk, self.w_uk_t)
         o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
         K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
                            self.position.interleaved, o_lat, kr, r, self.scale, self.window,
-                           inv_freq_lo=getattr(self.position, "inv_freq_lo", None), n_splits=self._n_splits(n, ctx.max_kv))
+                           inv_freq_lo=lo, n_splits=self._n_splits(n, ctx.max_kv))
         o = self._per_head(o_lat, self.w_uv.transpose(1, 2), self.w_uv)
         out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
         K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)

@@ -77,6 +77,11 @@ CONFIGS: Dict[str, dict] = {
                         latent(heads=5, dim=6, rot_dim=0, vdim=10, q_rank=33, kv_rank=17, window=None),
                         latent(heads=1, dim=10, rot_dim=2, vdim=3, q_rank=9, kv_rank=70, window=97, limit=None)],
                        width=56, vocab=211, streams=3, mult=1.0),
+    # head sizes in steps of 16: in bfloat16 a prompt from position 0 takes the tensor-core prompt attention (values narrower
+    # than the head, as wide as it, no rotated part), every later piece and token the kernel over the cached latents
+    "lat_tc": config([latent(heads=3, dim=24, rot_dim=8, vdim=16, q_rank=20, kv_rank=40, window=70),
+                      latent(heads=2, dim=16, rot_dim=0, vdim=16, q_rank=24, kv_rank=32, window=None, ff=None),
+                      latent(heads=4, dim=8, rot_dim=8, vdim=8, q_rank=16, kv_rank=16, window=130)], width=64, vocab=173, streams=2),
     "rec": config([rglru()], streams=None),
     "rec_taps": config([rglru(width=40, conv=1, blocks=1, ff=None), rglru(width=35, conv=5, blocks=5), rglru(width=64, conv=2, blocks=2)],
                        width=40, streams=4, bigram=(13, 3, 1), emb_scale=1.0),
