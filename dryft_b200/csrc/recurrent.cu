@@ -209,9 +209,9 @@ __global__ void __launch_bounds__(CK_THREADS) retention_chunk_state_kernel(
 #pragma unroll
       for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
     for (int j = 0; j < L; ++j) {
-      float kv[8], vv[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { kv[i] = ks[j * dP + d0 + i]; vv[i] = vs[j * vP + v0 + i]; }
+      const float4 k0 = *reinterpret_cast<const float4*>(ks + j * dP + d0), k1 = *reinterpret_cast<const float4*>(ks + j * dP + d0 + 4);
+      const float4 u0 = *reinterpret_cast<const float4*>(vs + j * vP + v0), u1 = *reinterpret_cast<const float4*>(vs + j * vP + v0 + 4);
+      const float kv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w}, vv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -277,10 +277,11 @@ __global__ void __launch_bounds__(CK_THREADS) retention_chunk_out_kernel(
   const int dQ = ((dim + 3) & ~3) + 1;           // odd row length: rows of q and k fall on different banks
   const int vP = (vdim + 3) & ~3;
   const int stage = max(CH * dQ, CH * vP);       // the q rows' place also holds the outputs before the norm
-  float* qs = smem;                  // [CH][dQ], later o [CH][vP]
+  float* vs = smem;                  // [CH][vP]            (16-byte rows first)
+  float* slab = vs + CH * vP;        // [SLAB][vP]          a slab of the state the chunk starts from
+  float* qs = slab + 16 * vP;        // [CH][dQ], later o [CH][vP]
   float* ks = qs + stage;            // [CH][dQ]
-  float* vs = ks + CH * dQ;          // [CH][vP]
-  float* A = vs + CH * vP;           // [CH][CH + 1]
+  float* A = ks + CH * dQ;           // [CH][CH + 1]
   float* pw = A + CH * (CH + 1);     // [CH + 1]
   for (int i = threadIdx.x; i <= CH; i += CK_THREADS) pw[i] = (float)pow(decay[hd], (double)i);
   load_rotated<T>(qs, dQ, proj, ld, q_off + hd * dim, n_first, L, dim, rot, inv_freq, inv_freq_lo, tok_pos, 1.f);
@@ -319,50 +320,90 @@ __global__ void __launch_bounds__(CK_THREADS) retention_chunk_out_kernel(
       }
   }
   __syncthreads();
-  // o = w^(i+1) (q S_in) + A v : 8 rows x 4 columns a thread, kept in registers until every thread has read q
+  // o = w^(i+1) (q S_in) + A v : 8 rows x 4 columns a thread, kept in registers until every thread has read q.
+  // S_in comes through shared memory in slabs of SLAB key rows; the next slab is asked for (into registers) before the
+  // current one is multiplied, so its trip from L2 hides behind the products.
   const float* S_in = sbuf + ((size_t)g * H + hd) * dim * vdim;
   const int tv = vP / 4, n_tiles = (CH / 8) * tv;
   constexpr int MAX_TILES = 4;       // tiles a thread may hold (value sizes up to 512)
+  constexpr int SLAB = 16, SLAB_LOADS = (SLAB * 512 / 4 + CK_THREADS - 1) / CK_THREADS;   // float4 pieces a thread fetches
   float acc[MAX_TILES][8][4];
-  int n_mine = 0;
-  for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
-    const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
-    float (*a)[4] = acc[n_mine];
+#pragma unroll
+  for (int t = 0; t < MAX_TILES; ++t)
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) a[r][c] = 0.f;
-    if (i0 >= L) continue;
-    for (int d = 0; d < dim; ++d) {
-      float sv[4];
+      for (int c = 0; c < 4; ++c) acc[t][r][c] = 0.f;
+  const int slab_vec = SLAB * tv;    // float4 pieces of a slab [SLAB][vP]
+  const bool rows_vec = (vdim & 3) == 0;
+  float4 pre[SLAB_LOADS];
+  auto fetch = [&](int d0) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) sv[c] = v0 + c < vdim ? __ldg(S_in + (size_t)d * vdim + v0 + c) : 0.f;
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float qv = qs[(i0 + r) * dQ + d];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) a[r][c] = fmaf(qv, sv[c], a[r][c]);
+    for (int u = 0; u < SLAB_LOADS; ++u) {
+      const int idx = threadIdx.x + u * CK_THREADS;
+      pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (idx < slab_vec) {
+        const int dd = d0 + idx / tv, v = (idx % tv) * 4;
+        if (dd < dim) {
+          const float* src = S_in + (size_t)dd * vdim + v;
+          if (rows_vec) pre[u] = __ldg(reinterpret_cast<const float4*>(src));
+          else pre[u] = make_float4(v < vdim ? __ldg(src) : 0.f, v + 1 < vdim ? __ldg(src + 1) : 0.f,
+                                    v + 2 < vdim ? __ldg(src + 2) : 0.f, v + 3 < vdim ? __ldg(src + 3) : 0.f);
+        }
       }
     }
+  };
+  fetch(0);
+  for (int d0 = 0; d0 < dim; d0 += SLAB) {
+    __syncthreads();   // the slab before is used up
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
+    for (int u = 0; u < SLAB_LOADS; ++u) {
+      const int idx = threadIdx.x + u * CK_THREADS;
+      if (idx < slab_vec) *reinterpret_cast<float4*>(slab + (size_t)idx * 4) = pre[u];
+    }
+    __syncthreads();
+    if (d0 + SLAB < dim) fetch(d0 + SLAB);
+    const int d_end = min(SLAB, dim - d0);
+    int n_mine = 0;
+    for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
+      const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
+      if (i0 >= L) continue;
+      float (*a)[4] = acc[n_mine];
+      for (int dd = 0; dd < d_end; ++dd) {
+        const float4 sv = *reinterpret_cast<const float4*>(slab + (size_t)dd * vP + v0);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) a[r][c] *= pw[i0 + r + 1];
-    const int j_end = min(L, i0 + 8);
-    for (int j = 0; j < j_end; ++j) {
-      float vv[4];
+        for (int r = 0; r < 8; ++r) {
+          const float qv = qs[(i0 + r) * dQ + d0 + dd];
+          a[r][0] = fmaf(qv, sv.x, a[r][0]); a[r][1] = fmaf(qv, sv.y, a[r][1]);
+          a[r][2] = fmaf(qv, sv.z, a[r][2]); a[r][3] = fmaf(qv, sv.w, a[r][3]);
+        }
+      }
+    }
+  }
+  {
+    int n_mine = 0;
+    for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
+      const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
+      if (i0 >= L) continue;
+      float (*a)[4] = acc[n_mine];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) vv[c] = vs[j * vP + v0 + c];
+      for (int r = 0; r < 8; ++r)
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float av = A[(i0 + r) * (CH + 1) + j];
+        for (int c = 0; c < 4; ++c) a[r][c] *= pw[i0 + r + 1];
+      const int j_end = min(L, i0 + 8);
+      for (int j = 0; j < j_end; ++j) {
+        const float4 vv = *reinterpret_cast<const float4*>(vs + (size_t)j * vP + v0);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) a[r][c] = fmaf(av, vv[c], a[r][c]);
+        for (int r = 0; r < 8; ++r) {
+          const float av = A[(i0 + r) * (CH + 1) + j];
+          a[r][0] = fmaf(av, vv.x, a[r][0]); a[r][1] = fmaf(av, vv.y, a[r][1]);
+          a[r][2] = fmaf(av, vv.z, a[r][2]); a[r][3] = fmaf(av, vv.w, a[r][3]);
+        }
       }
     }
   }
   __syncthreads();   // q is read by all: its place takes the outputs
-  n_mine = 0;
+  int n_mine = 0;
   for (int tile = threadIdx.x; tile < n_tiles && n_mine < MAX_TILES; tile += CK_THREADS, ++n_mine) {
     const int i0 = (tile / tv) * 8, v0 = (tile % tv) * 4;
 #pragma unroll
@@ -562,7 +603,7 @@ DRYFT_API int dryft_retention_chunked(int is_bf16, const void* proj, int ld, int
   const size_t smem_a = sizeof(float) * ((size_t)CH * dP + (size_t)CH * vP8 + CH + 1);
   const int dQ = ((dim + 3) & ~3) + 1, vP = (vdim + 3) & ~3;
   const size_t stage = (size_t)CH * (dQ > vP ? dQ : vP);
-  const size_t smem_c = sizeof(float) * (stage + (size_t)CH * dQ + (size_t)CH * vP + (size_t)CH * (CH + 1) + CH + 1);
+  const size_t smem_c = sizeof(float) * (stage + (size_t)CH * dQ + (size_t)(CH + 16) * vP + (size_t)CH * (CH + 1) + CH + 1);
   int rc = is_bf16 ? opt_in_smem(retention_chunk_state_kernel<bf>, smem_a) : opt_in_smem(retention_chunk_state_kernel<float>, smem_a);
   if (rc) return rc;
   rc = is_bf16 ? opt_in_smem(retention_chunk_out_kernel<bf>, smem_c) : opt_in_smem(retention_chunk_out_kernel<float>, smem_c);

@@ -1370,11 +1370,12 @@ def retention_scan(proj, offsets, cu_q, seq_slot, tok_pos, inv_freq, rot: int, d
         lib = recurrent_lib()
         ch = int(lib.dryft_retention_chunk_tokens())
         sbuf = torch.empty((n // ch + n_seqs) * heads * dim * vdim, dtype=torch.float32, device=proj.device)
-        _ok(lib.dryft_retention_chunked(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
-                                        _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state),
-                                        _ptr(sbuf), _ptr(out), n, n_seqs, heads, dim, vdim, float(k_scale), float(eps), _stream()),
-            f"retention_chunked ({heads} heads of {dim} x {vdim})", n_kernels=3)
-        return
+        rc = lib.dryft_retention_chunked(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
+                                         _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state),
+                                         _ptr(sbuf), _ptr(out), n, n_seqs, heads, dim, vdim, float(k_scale), float(eps), _stream())
+        if rc != UNSUPPORTED:   # sizes whose chunk does not fit its shared memory are walked token by token below
+            _ok(rc, f"retention_chunked ({heads} heads of {dim} x {vdim})", n_kernels=3)
+            return
     _ok(recurrent_lib().dryft_retention_scan(_act(proj, "proj"), _ptr(proj), ld, q_off, k_off, v_off, g_off, _ptr(cu_q), _ptr(seq_slot),
                                              _ptr(tok_pos), _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(rot), _ptr(decay), _ptr(state), _ptr(out), n_seqs,
                                              heads, dim, vdim, float(k_scale), float(eps), _stream()),
