@@ -289,28 +289,47 @@ __global__ void __launch_bounds__(WPB * 32) latent_attn_rows_kernel(
   }
 }
 
-// o_lat[h, n, :] from the splits' (max, sum, weighted sum): one block per (token, head)
+// o_lat[h, n, :] from the splits' (max, sum, weighted sum): one block per (token, head).  The first warp turns the splits'
+// maxima and sums into one weight per split (up to MAX_SPLITS of them); every thread then sums its latent entries.
+constexpr int MAX_SPLITS = 64;
+
 template <typename T>
 __global__ void latent_combine_kernel(const float* __restrict__ part, const int* __restrict__ tok_slot, T* __restrict__ o_lat,
                                       int n_splits, int n_tokens, int H, int kv_rank) {
+  __shared__ float w[MAX_SPLITS];
   const int n = blockIdx.x, hd = blockIdx.y;
   if (tok_slot[n] < 0) return;
-  const float* src = part + ((size_t)n * H + hd) * n_splits * (kv_rank + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[(size_t)s * (kv_rank + 2)]);
-  float l = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = src[(size_t)s * (kv_rank + 2)];
-    if (ms > -INFINITY) l += src[(size_t)s * (kv_rank + 2) + 1] * expf(ms - m);
+  const size_t stride = (size_t)kv_rank + 2;
+  const float* src = part + ((size_t)n * H + hd) * n_splits * stride;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float ms[MAX_SPLITS / 32], ls[MAX_SPLITS / 32];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < MAX_SPLITS / 32; ++u) {
+      const int sidx = lane + 32 * u;
+      ms[u] = sidx < n_splits ? src[sidx * stride] : -INFINITY;
+      ls[u] = sidx < n_splits ? src[sidx * stride + 1] : 0.f;
+      m = fmaxf(m, ms[u]);
+    }
+    m = warp_max(m);
+    float l = 0.f;
+#pragma unroll
+    for (int u = 0; u < MAX_SPLITS / 32; ++u) {
+      ms[u] = ms[u] > -INFINITY ? expf(ms[u] - m) : 0.f;   // a split without keys weighs nothing
+      l = fmaf(ls[u], ms[u], l);
+    }
+    l = warp_sum(l);
+#pragma unroll
+    for (int u = 0; u < MAX_SPLITS / 32; ++u)
+      if (lane + 32 * u < n_splits) w[lane + 32 * u] = ms[u] / l;
   }
-  const float inv = 1.f / l;
+  __syncthreads();
   for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = src[(size_t)s * (kv_rank + 2)];
-      if (ms > -INFINITY) a = fmaf(src[(size_t)s * (kv_rank + 2) + 2 + d], expf(ms - m), a);
-    }
-    o_lat[((size_t)hd * n_tokens + n) * kv_rank + d] = from_f32<T>(a * inv);
+#pragma unroll 8
+    for (int sidx = 0; sidx < n_splits; ++sidx) a = fmaf(src[sidx * stride + 2 + d], w[sidx], a);
+    o_lat[((size_t)hd * n_tokens + n) * kv_rank + d] = from_f32<T>(a);
   }
 }
 
@@ -457,7 +476,7 @@ DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void
                                      int rot, float scale, int window, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (kv_rank <= 0 || kv_rank > 512 || rot < 0 || (rot & 1) || H <= 0 || (H + HPB - 1) / HPB > 65535) return DRYFT_ERR_UNSUPPORTED;
-  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && !part)) return DRYFT_ERR_UNSUPPORTED;
+  if (n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && !part)) return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
   const int nr = (kv_rank + 31) / 32;
 #define DRYFT_LATENT_ROWS(NR)                                                                                                      \
