@@ -96,14 +96,15 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename T>
+// MS: the most streams this instantiation holds in registers (1, 2, 4 or MAX_STREAMS); fewer registers, more blocks an SM
+template <typename T, int MS>
 __global__ void __launch_bounds__(THREADS) hc_step_kernel(
     const float* __restrict__ x_in, int s_in, float* __restrict__ x_out, int S, const T* __restrict__ y,
     const float* __restrict__ mix, const float* __restrict__ outw, float mult, const float* __restrict__ inw,
     const float* __restrict__ norm_w, float eps, const int* __restrict__ rows, T* __restrict__ h, int width) {
   extern __shared__ __align__(16) float row[];
   __shared__ float scratch[33];
-  __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+  __shared__ float c_mix[MS * MS], c_out[MS], c_in[MS];
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   if (threadIdx.x < S * S) c_mix[threadIdx.x] = y ? mix[threadIdx.x] : 0.f;
@@ -116,19 +117,19 @@ __global__ void __launch_bounds__(THREADS) hc_step_kernel(
   if ((width & 3) == 0) {
     // four columns a thread, 16-byte accesses to the streams: the pass is bound by bytes in flight
     for (int c = threadIdx.x * 4; c < width; c += THREADS * 4) {
-      float4 x[MAX_STREAMS];
+      float4 x[MS];
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) x[s] = *reinterpret_cast<const float4*>(x_in + (src * s_in + (s_in == 1 ? 0 : s)) * width + c);
       if (y) {
         const float4 yv = load4<T>(y + src * width + c);
-        float4 xn[MAX_STREAMS];
+        float4 xn[MS];
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t) {
+        for (int t = 0; t < MS; ++t) {
           if (t < S) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; ++s)
+            for (int s = 0; s < MS; ++s)
               if (s < S) {
                 const float m = c_mix[s * S + t];
                 acc.x = fmaf(m, x[s].x, acc.x); acc.y = fmaf(m, x[s].y, acc.y); acc.z = fmaf(m, x[s].z, acc.z); acc.w = fmaf(m, x[s].w, acc.w);
@@ -138,18 +139,18 @@ __global__ void __launch_bounds__(THREADS) hc_step_kernel(
           }
         }
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t)
+        for (int t = 0; t < MS; ++t)
           if (t < S) x[t] = xn[t];
       }
       if (x_out) {
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t)
+        for (int t = 0; t < MS; ++t)
           if (t < S) *reinterpret_cast<float4*>(x_out + (src * S + t) * width + c) = x[t];
       }
       if (inw) {
         float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t)
+        for (int t = 0; t < MS; ++t)
           if (t < S) {
             const float w = c_in[t];
             u.x = fmaf(w, x[t].x, u.x); u.y = fmaf(w, x[t].y, u.y); u.z = fmaf(w, x[t].z, u.z); u.w = fmaf(w, x[t].w, u.w);
@@ -168,36 +169,36 @@ __global__ void __launch_bounds__(THREADS) hc_step_kernel(
     return;
   }
   for (int c = threadIdx.x; c < width; c += THREADS) {
-    float x[MAX_STREAMS];
+    float x[MS];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s)
+    for (int s = 0; s < MS; ++s)
       if (s < S) x[s] = x_in[(src * s_in + (s_in == 1 ? 0 : s)) * width + c];
     if (y) {
       const float yv = to_f32<T>(y[src * width + c]);
-      float xn[MAX_STREAMS];
+      float xn[MS];
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) {
+      for (int t = 0; t < MS; ++t) {
         if (t < S) {
           float acc = 0.f;
 #pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s)
+          for (int s = 0; s < MS; ++s)
             if (s < S) acc = fmaf(c_mix[s * S + t], x[s], acc);
           xn[t] = fmaf(c_out[t], yv, acc);
         }
       }
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t)
+      for (int t = 0; t < MS; ++t)
         if (t < S) x[t] = xn[t];
     }
     if (x_out) {
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t)
+      for (int t = 0; t < MS; ++t)
         if (t < S) x_out[(src * S + t) * width + c] = x[t];
     }
     if (inw) {
       float u = 0.f;
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t)
+      for (int t = 0; t < MS; ++t)
         if (t < S) u = fmaf(c_in[t], x[t], u);
       row[c] = u;
       ss = fmaf(u, u, ss);
@@ -280,14 +281,24 @@ DRYFT_API int dryft_hc_step(int is_bf16, const float* x_in, int s_in, float* x_o
   if (inw && (!norm_w || !h)) return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
   const size_t smem = sizeof(float) * (size_t)width;
-  int rc = is_bf16 ? row_smem(hc_step_kernel<bf>, width) : row_smem(hc_step_kernel<float>, width);
-  if (rc) return rc;
-  if (is_bf16)
-    hc_step_kernel<bf><<<n_rows, THREADS, smem, st>>>(x_in, s_in, x_out, n_streams, (const bf*)y, mix, outw, mult, inw, norm_w, eps,
-                                                      rows, (bf*)h, width);
-  else
-    hc_step_kernel<float><<<n_rows, THREADS, smem, st>>>(x_in, s_in, x_out, n_streams, (const float*)y, mix, outw, mult, inw, norm_w,
-                                                         eps, rows, (float*)h, width);
+#define DRYFT_HC_LAUNCH(TT, MS)                                                                                                  \
+  do {                                                                                                                          \
+    int rc = row_smem(hc_step_kernel<TT, MS>, width);                                                                           \
+    if (rc) return rc;                                                                                                          \
+    hc_step_kernel<TT, MS><<<n_rows, THREADS, smem, st>>>(x_in, s_in, x_out, n_streams, (const TT*)y, mix, outw, mult, inw, norm_w, \
+                                                          eps, rows, (TT*)h, width);                                            \
+  } while (0)
+#define DRYFT_HC_BY_STREAMS(TT)                                                                                                  \
+  do {                                                                                                                          \
+    if (n_streams <= 1) DRYFT_HC_LAUNCH(TT, 1);                                                                                 \
+    else if (n_streams <= 2) DRYFT_HC_LAUNCH(TT, 2);                                                                            \
+    else if (n_streams <= 4) DRYFT_HC_LAUNCH(TT, 4);                                                                            \
+    else DRYFT_HC_LAUNCH(TT, MAX_STREAMS);                                                                                      \
+  } while (0)
+  if (is_bf16) DRYFT_HC_BY_STREAMS(bf);
+  else DRYFT_HC_BY_STREAMS(float);
+#undef DRYFT_HC_BY_STREAMS
+#undef DRYFT_HC_LAUNCH
   return launch_status();
 }
 
