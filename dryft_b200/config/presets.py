@@ -97,22 +97,22 @@ def _vobusun(width: int, heads: int, head_dim: int, ff: int, vocab: int, repeats
              rot_dim: int, rec_blocks: int, streams: int = 4) -> dict:
     """A Vobusun ``config.json``: a group of four layers (gated recurrence, two retention layers, latent attention) run
     ``repeats`` times, every run after the first with the first group's weights and a state of its own."""
-    decay = [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, heads - 1)) for h in range(heads)]
+    decay = [1.0 - 2.0 ** (-4.5 - 6.0 * h / max(1, heads - 1)) for h in range(heads)]   # memories of 20 to 1,400 tokens
     mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
     ret = {"type": "retention", "mlp": mlp,
-           "mixer": {"heads": heads, "dim": head_dim, "vdim": head_dim, "decay": decay, "rot": {"dims": head_dim, "base": 1000000.0}}}
+           "mixer": {"heads": heads, "dim": head_dim, "vdim": head_dim, "decay": decay, "rot": {"dims": head_dim, "base": 500000.0}}}
     group = [
         {"type": "rglru", "mixer": {"width": width, "conv": 4, "blocks": rec_blocks}, "mlp": mlp},
         ret, ret,
         {"type": "latent_attention", "mlp": mlp,
          "mixer": {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank,
-                   "scale": (head_dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 10000.0}, "mask": {"size": window}}},
+                   "scale": (head_dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 20000.0}, "mask": {"size": window}}},
     ]
     layers = [dict(l) for l in group]
     for _ in range(repeats - 1):
         layers += [dict(l, weights_of=j) for j, l in enumerate(group)]
     return {"architecture": "Vobusun", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 1009, "mul_cur": 31}},
-            "norm": {"eps": 1e-6}, "residual_mult": 0.7, "streams": streams, "layers": layers}
+            "norm": {"eps": 1e-5}, "residual_mult": 0.5, "streams": streams, "layers": layers}
 
 
 # Vobusun shapes with layers the size of a real model's, and beside each the dense Qwen3 shape of equal size (the same width,

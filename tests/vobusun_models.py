@@ -13,7 +13,7 @@ from tevovik_models import prompts, row_errors, write_model  # noqa: F401  (shar
 
 def retention(heads=3, dim=16, vdim=24, rot_dims: Optional[int] = 8, base=500.0, decay=None, ff: Optional[int] = 40, limit=0.8, **kw) -> dict:
     mixer = {"heads": heads, "dim": dim, "vdim": vdim,
-             "decay": decay if decay is not None else [1.0 - 2.0 ** -(3 + 2 * h) for h in range(heads)]}
+             "decay": decay if decay is not None else [1.0 - 0.3 ** (h + 1.5) for h in range(heads)]}
     if rot_dims:
         mixer["rot"] = {"dims": rot_dims, "base": base}
     return _layer("retention", mixer, ff, limit, **kw)
@@ -85,7 +85,7 @@ CONFIGS: Dict[str, dict] = {
     "rec": config([rglru()], streams=None),
     "rec_taps": config([rglru(width=40, conv=1, blocks=1, ff=None), rglru(width=35, conv=5, blocks=5), rglru(width=64, conv=2, blocks=2)],
                        width=40, streams=4, bigram=(13, 3, 1), emb_scale=1.0),
-    "mixed": config(_mixed(), width=64, vocab=157, streams=3, mult=0.7),
+    "mixed": config(_mixed(), width=64, vocab=157, streams=3, mult=0.8),
 }
 
 
