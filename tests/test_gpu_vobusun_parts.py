@@ -148,12 +148,12 @@ def test_retention_keeps_one_far_key_among_hundreds_and_splits_anywhere(H, d, dv
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("kv_rank, rot, interleaved, window", [(24, 4, True, 20), (40, 16, False, 64), (70, 2, True, 97), (17, 0, True, 0),
-                                                              (512, 64, True, 130)])
-def test_latent_attention_one_key_stands_out_at_every_edge(dtype, kv_rank, rot, interleaved, window):
+@pytest.mark.parametrize("kv_rank, rot, interleaved, window, H", [(24, 4, True, 20, 3), (40, 16, False, 64, 3), (70, 2, True, 97, 1),
+                                                                 (17, 0, True, 0, 5), (512, 64, True, 130, 3), (32, 8, True, 50, 18)])
+def test_latent_attention_one_key_stands_out_at_every_edge(dtype, kv_rank, rot, interleaved, window, H):
     """Query positions around the window's edge and the page borders; the key at ``mark`` has a score far above all
     others, so the output is that key's latent exactly while it is visible and something else once it is not."""
-    H, page, Dk = 3, 64, kv_rank + rot
+    page, Dk = 64, kv_rank + rot      # 18 heads: two blocks of heads, the second with a warp of two heads and two warps of none
     n_pos = 300
     pages = 8
     k_pages = torch.full((pages, 1, page, Dk), float("nan"), device=DEV, dtype=dtype)      # poisoned: unread rows stay NaN
