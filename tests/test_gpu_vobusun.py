@@ -268,3 +268,76 @@ def test_forty_unequal_requests_at_once(tmp_path_factory, dtype):
         pairs += [(torch.cat(r), plain_logits(entry, reqs[b])[heads[b]:], f"request {b}") for b, r in rows.items() if r]
     close_all(pairs, dtype, "forty requests")
     eng.cache.check()
+
+
+def _random_config(seed):
+    """A configuration drawn at random: layer kinds and order, every size, every constant, which options are absent."""
+    import random
+
+    r = random.Random(seed)
+    even = lambda lo, hi: 2 * r.randint(lo // 2, hi // 2)
+    layers = []
+    for _ in range(r.randint(2, 4)):
+        kind = r.choice(["retention", "latent", "rglru"])
+        ff = r.choice([None, r.randint(6, 50)])
+        limit = r.choice([None, round(r.uniform(0.4, 3.0), 3)])
+        if kind == "retention":
+            heads, dim = r.randint(1, 5), r.randint(2, 36)
+            layers.append(M.retention(heads=heads, dim=dim, vdim=r.randint(2, 40), rot_dims=r.choice([None, even(2, dim)]) if dim >= 2 else None,
+                                      base=r.choice([37.0, 1000.0, 250000.0]), decay=[round(r.uniform(0.8, 0.9997), 6) for _ in range(heads)],
+                                      ff=ff, limit=limit))
+        elif kind == "latent":
+            rot = r.choice([0, even(2, 16)])
+            layers.append(M.latent(heads=r.randint(1, 6), dim=r.randint(3, 30), rot_dim=rot, vdim=r.randint(2, 36), q_rank=r.randint(4, 40),
+                                   kv_rank=r.randint(4, 70), window=r.choice([None, r.randint(1, 150)]), base=r.choice([25.0, 5000.0]),
+                                   scale=round(r.uniform(0.1, 0.4), 4), ff=ff, limit=limit))
+        else:
+            blocks = r.randint(1, 4)
+            layers.append(M.rglru(width=blocks * r.randint(2, 18), conv=r.randint(1, 5), blocks=blocks, ff=ff, limit=limit))
+    for _ in range(r.randint(0, 3)):       # layers that run another layer's weights, anywhere in the order
+        j = r.randrange(len(layers))
+        if layers[j].get("weights_of") is None:
+            layers.append(M.again(layers, j))
+    return M.config(layers, width=r.choice([24, 36, 50, 52, 64]), vocab=r.randint(40, 300), emb_scale=round(r.uniform(0.5, 9.0), 3),
+                    eps=r.choice([1e-6, 1e-5, 3e-4]), mult=round(r.uniform(0.3, 1.2), 3), streams=r.choice([None, 1, 2, 3, 5]),
+                    bigram=r.choice([None, (r.randint(3, 400), r.randint(1, 100000), r.randint(1, 999))]))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    cfg = _random_config(seed)
+    tensors = M.draw_weights(cfg, seed=100 + seed)
+    entry = (cfg, tensors, M.write_model(cfg, tensors, str(tmp_path / "m")), {})
+    reqs = M.prompts(cfg, [70, 1, 33], seed=seed)
+    for dtype in DTYPES:
+        eng = engine(entry, dtype, max_batch=4, max_seq_len=256, max_tokens=1024)
+        with torch.inference_mode():
+            heads = [max(1, len(t) - 6) for t in reqs]
+            slots = eng.cache.open_sequences(len(reqs))
+            got = eng.stepper.step(slots, [t[:h] for t, h in zip(reqs, heads)], [list(range(h)) for h in heads])
+            at, pairs = 0, []
+            for t, h in zip(reqs, heads):
+                pairs.append((got[at:at + h], plain_logits(entry, t)[:h], f"prompt of {h}"))
+                at += h
+            live, step, rows = [b for b in range(len(reqs)) if heads[b] < len(reqs[b])], 0, {b: [] for b in range(len(reqs))}
+            eng.cache.close_sequences([slots[b] for b in range(len(reqs)) if b not in live])
+            while live:
+                out = eng.stepper.step([slots[b] for b in live], [[reqs[b][heads[b] + step]] for b in live], [[0]] * len(live))
+                for i, b in enumerate(live):
+                    rows[b].append(out[i:i + 1])
+                step += 1
+                done = [b for b in live if heads[b] + step >= len(reqs[b])]
+                eng.cache.close_sequences([slots[b] for b in done])
+                live = [b for b in live if b not in done]
+            pairs += [(torch.cat(v), plain_logits(entry, reqs[b])[heads[b]:], f"request {b} decoded") for b, v in rows.items() if v]
+        what = f"random configuration {seed} ({[l['type'] for l in cfg['layers']]})"
+        if dtype == "float32":
+            close_all(pairs, dtype, what)
+        else:
+            # latents of four entries and widths of 24 make bfloat16 rounding large in some of these models: the sharp
+            # comparison is the 32-bit one; here the typical row must be close and every row finite
+            got_all = torch.cat([g.detach().float().cpu() for g, _, _ in pairs])
+            assert torch.isfinite(got_all).all(), what
+            e = M.row_errors(got_all, torch.cat([w for _, w, _ in pairs]))
+            assert float(e.median()) <= M.BF16_TOL, f"{what}: median row off by {float(e.median()):.3g}"
+        eng.cache.check()
