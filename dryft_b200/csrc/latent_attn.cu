@@ -418,6 +418,44 @@ __global__ void head_gate_rows_kernel(const T* __restrict__ o, int hd, const T* 
   out[i] = from_f32<T>(val);
 }
 
+// The per-head key and value matrices folded into the query and the output, for steps of few tokens and for the 32-bit
+// path (sums in a fixed order, so a row's result does not depend on its company):
+//   latent_fold_q     q_lat[h, n, r] = sum_d q[n, h, d] * w_k[h, d, r]                      (32-bit result)
+//   latent_unfold_o   out[n, h*V + v] = T( sigmoid(gate[n, h]) * sum_r o_lat[h, n, r] * w_v[h, r, v] )
+// One block per (token, head); a thread per output entry reads along the matrices' rows.
+template <typename T>
+__global__ void latent_fold_q_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ w, float* __restrict__ q_lat,
+                                     int n_tokens, int H, int dim, int kv_rank) {
+  extern __shared__ __align__(16) float vin[];
+  const int n = blockIdx.x, h = blockIdx.y;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) vin[d] = to_f32<T>(q[((size_t)n * H + h) * q_stride + d]);
+  __syncthreads();
+  const T* wh = w + (size_t)h * dim * kv_rank;
+  for (int r = threadIdx.x; r < kv_rank; r += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < dim; ++d) acc = fmaf(vin[d], to_f32<T>(wh[(size_t)d * kv_rank + r]), acc);
+    q_lat[((size_t)h * n_tokens + n) * kv_rank + r] = acc;
+  }
+}
+
+template <typename T>
+__global__ void latent_unfold_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ w, const T* __restrict__ gate,
+                                       int gate_ld, T* __restrict__ out, int n_tokens, int H, int kv_rank, int vdim) {
+  extern __shared__ __align__(16) float vin[];
+  const int n = blockIdx.x, h = blockIdx.y;
+  for (int r = threadIdx.x; r < kv_rank; r += blockDim.x) vin[r] = to_f32<T>(o_lat[((size_t)h * n_tokens + n) * kv_rank + r]);
+  __syncthreads();
+  const float g = gate ? 1.f / (1.f + expf(-to_f32<T>(gate[(size_t)n * gate_ld + h]))) : 1.f;
+  const T* wh = w + (size_t)h * kv_rank * vdim;
+  for (int v = threadIdx.x; v < vdim; v += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < kv_rank; ++r) acc = fmaf(vin[r], to_f32<T>(wh[(size_t)r * vdim + v]), acc);
+    out[((size_t)n * H + h) * vdim + v] = from_f32<T>(acc * g);
+  }
+}
+
 template <typename K> int opt_in(K kernel, size_t bytes) {
   if (bytes > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (bytes > 48 * 1024) {
@@ -491,6 +529,36 @@ DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void
   if (nr <= 8) { DRYFT_LATENT_ROWS(8); }
   DRYFT_LATENT_ROWS(16);
 #undef DRYFT_LATENT_ROWS
+}
+
+DRYFT_API int dryft_latent_fold_q(int is_bf16, const void* q, int q_stride, const void* w, float* q_lat, int n_tokens, int H, int dim,
+                                  int kv_rank, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || H > 65535 || dim <= 0 || kv_rank <= 0 || dim > 12000) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int threads = kv_rank >= 256 ? 256 : (kv_rank >= 128 ? 128 : 64);
+  const size_t smem = sizeof(float) * (size_t)dim;
+  dim3 grid(n_tokens, H);
+  if (is_bf16) latent_fold_q_kernel<bf><<<grid, threads, smem, st>>>((const bf*)q, q_stride, (const bf*)w, q_lat, n_tokens, H, dim, kv_rank);
+  else latent_fold_q_kernel<float><<<grid, threads, smem, st>>>((const float*)q, q_stride, (const float*)w, q_lat, n_tokens, H, dim, kv_rank);
+  return launch_status();
+}
+
+DRYFT_API int dryft_latent_unfold_o(int is_bf16, const void* o_lat, const void* w, const void* gate, int gate_ld, void* out, int n_tokens,
+                                    int H, int kv_rank, int vdim, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || H > 65535 || vdim <= 0 || kv_rank <= 0 || kv_rank > 12000) return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  const int threads = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
+  const size_t smem = sizeof(float) * (size_t)kv_rank;
+  dim3 grid(n_tokens, H);
+  if (is_bf16)
+    latent_unfold_o_kernel<bf><<<grid, threads, smem, st>>>((const bf*)o_lat, (const bf*)w, (const bf*)gate, gate_ld, (bf*)out, n_tokens, H,
+                                                            kv_rank, vdim);
+  else
+    latent_unfold_o_kernel<float><<<grid, threads, smem, st>>>((const float*)o_lat, (const float*)w, (const float*)gate, gate_ld, (float*)out,
+                                                               n_tokens, H, kv_rank, vdim);
+  return launch_status();
 }
 
 DRYFT_API int dryft_latent_scratch_table(const int* cu_q, const int* seq_slot, int n_seqs, int* table, int max_pages, int page_size,

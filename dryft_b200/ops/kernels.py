@@ -1233,6 +1233,8 @@ def latent_attn_lib() -> ctypes.CDLL:
         "dryft_latent_scratch_table": [_p, _p, _i, _p, _i, _i, _p],
         "dryft_latent_expand_store": [_i, _p, _p, _i, _i, _p, _i, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p],
         "dryft_head_gate_rows": [_i, _p, _i, _p, _i, _p, _i, _i, _i, _p],
+        "dryft_latent_fold_q": [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p],
+        "dryft_latent_unfold_o": [_i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _p],
         "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
         "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
     })
@@ -1531,15 +1533,32 @@ def head_gate(o, gate, gate_col: int, out) -> None:
         "head_gate")
 
 
-def gemm_nt_f32_view(a, w, out) -> None:
-    """``gemm_nt_f32`` for 2-D views: ``a [M, K]`` and ``out [M, N]`` may be column ranges of wider rows (unit stride along
-    a row); ``w [N, K]`` is contiguous."""
-    m, k = a.shape
-    n = w.shape[0]
-    for t, nm in ((a, "a"), (out, "out")):
-        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
-            raise KernelError(f"gemm_nt_f32_view: {nm} must be a float32 CUDA matrix with unit stride along rows")
-    _need(w, "w", torch.float32, (n, k))
-    if out.shape != (m, n):
-        raise KernelError(f"gemm_nt_f32_view: out is {tuple(out.shape)}, expected {(m, n)}")
-    _ok(core().dryft_gemm_nt_f32(_ptr(a), a.stride(0), _ptr(w), _ptr(out), out.stride(0), m, n, k, _stream()), "gemm_nt_f32")
+def latent_fold_q(q, w_k, q_lat, dim: int) -> None:
+    """``q_lat[h, n, :] = q[n, h, :dim] @ w_k[h]`` with ``w_k [H, dim, kv_rank]``; float32 result, sums in a fixed order."""
+    n, n_heads, q_stride = q.shape
+    kv_rank = w_k.shape[2]
+    _need(q, "q")
+    _need(w_k, "w_k", q.dtype, (n_heads, dim, kv_rank))
+    _need(q_lat, "q_lat", torch.float32, (n_heads, n, kv_rank))
+    if dim > q_stride:
+        raise KernelError("latent_fold_q: the unrotated part lies outside the query rows")
+    _ok(latent_attn_lib().dryft_latent_fold_q(_act(q, "q"), _ptr(q), q_stride, _ptr(w_k), _ptr(q_lat), n, n_heads, dim, kv_rank, _stream()),
+        "latent_fold_q")
+
+
+def latent_unfold_o(o_lat, w_v, gate, gate_col: int, out) -> None:
+    """``out[n, h*V:(h+1)*V] = T(sigmoid(gate[n, gate_col + h]) * (o_lat[h, n] @ w_v[h]))`` with ``w_v [H, kv_rank, V]``
+    (``gate`` None: no gate)."""
+    n_heads, n, kv_rank = o_lat.shape
+    vdim = w_v.shape[2]
+    _need(o_lat, "o_lat")
+    _need(w_v, "w_v", o_lat.dtype, (n_heads, kv_rank, vdim))
+    _need(out, "out", o_lat.dtype, (n, n_heads * vdim))
+    gate_ptr, gate_ld = None, 0
+    if gate is not None:
+        _need(gate, "gate", out.dtype)
+        if gate.dim() != 2 or gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+            raise KernelError("latent_unfold_o: gate columns outside the gate tensor")
+        gate_ptr, gate_ld = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    _ok(latent_attn_lib().dryft_latent_unfold_o(_act(out, "out"), _ptr(o_lat), _ptr(w_v), gate_ptr, gate_ld, _ptr(out), n, n_heads, kv_rank,
+                                                vdim, _stream()), "latent_unfold_o")

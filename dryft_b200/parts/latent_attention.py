@@ -10,7 +10,8 @@ With ``H`` heads, per head ``d`` unrotated and ``r`` rotated query/key dims, val
 
 Only ``[c | k_rot]`` is cached, one row per token for all heads (a keys-only cache group).  The per-head key and value
 matrices are folded into the query and the output: ``q_lat = W_uk^T q_plain`` before attention, ``o = W_uv o_lat`` after,
-both as batched matrix products over the heads; attention itself runs over the cached rows (``csrc/latent_attn.cu``).
+as batched matrix products over the heads (steps of few tokens and the 32-bit path: kernels of this library); attention
+itself runs over the cached rows (``csrc/latent_attn.cu``).
 A bfloat16 step in which every sequence starts at position 0 (all its keys are its own) makes per-head keys and values
 from its latents by one more product and runs the library's tensor-core prompt attention over pages of the step's own;
 every other step (a piece that continues a prompt, a single token, everything in 32-bit) runs over the cached latents.
@@ -88,10 +89,9 @@ class LatentAttention:
         H, d, dv, kr = self.n_heads, self.qk_dim, self.v_dim, self.kv_rank
         w_uk = weights.load(nm["uk"], "matrix")      # [H*d, kr]
         w_uv = weights.load(nm["uv"], "matrix")      # [H*dv, kr]
-        # per head: q_lat = q_plain @ W_uk,h ([d, kr]) and o = o_lat @ W_uv,h^T ([kr, dv])
+        # per head: q_lat = q_plain @ W_uk,h ([d, kr]) and o = o_lat @ W_uv,h^T ([kr, dv]), both with the input index first
         self.w_uk = w_uk.reshape(H, d, kr).contiguous()
-        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()        # [H, kr, d]: rows = outputs, for the 32-bit product
-        self.w_uv = w_uv.reshape(H, dv, kr).contiguous()            # [H, dv, kr]: rows = outputs
+        self.w_uv_t = w_uv.reshape(H, dv, kr).transpose(1, 2).contiguous()
         K.latent_attn_lib()
         # prompts whose sequences all start at position 0 (bfloat16): keys and values per head from the step's own latents
         # (one product), then the library's tensor-core prompt attention over pages of the step's own
@@ -137,14 +137,23 @@ class LatentAttention:
             out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
             K.head_gate_rows(o_pad, proj if self.has_gate else None, self.gate_col, out, H, dv)
             return linear(out, self.w_o, self.rt)
-        q_lat = self._per_head(q[:, :, :d].transpose(0, 1), self.w_uk, self.w_uk_t)
+        # few tokens, and everything in 32-bit: kernels of this library (sums in a fixed order, the same whether the step is
+        # captured in a graph or not); bfloat16 steps of many tokens: one batched library product over the heads
+        own = h.dtype == torch.float32 or n <= self.rt.small_m_max
+        if own:
+            q_lat = torch.empty((H, n, kr), dtype=torch.float32, device=dev)
+            K.latent_fold_q(q, self.w_uk, q_lat, d)
+        else:
+            q_lat = torch.bmm(q[:, :, :d].transpose(0, 1), self.w_uk, out_dtype=torch.float32)
         o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
         K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
                            self.position.interleaved, o_lat, kr, r, self.scale, self.window,
                            inv_freq_lo=lo, n_splits=self._n_splits(n, ctx.max_kv))
-        o = self._per_head(o_lat, self.w_uv.transpose(1, 2), self.w_uv)
         out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
-        K.head_gate(o, proj if self.has_gate else None, self.gate_col, out)
+        if own:
+            K.latent_unfold_o(o_lat, self.w_uv_t, proj if self.has_gate else None, self.gate_col, out)
+        else:
+            K.head_gate(torch.bmm(o_lat, self.w_uv_t, out_dtype=torch.float32), proj if self.has_gate else None, self.gate_col, out)
         return linear(out, self.w_o, self.rt)
 
     HEADS_PER_BLOCK, KEYS_PER_TILE = 16, 32     # csrc/latent_attn.cu
@@ -156,14 +165,3 @@ class LatentAttention:
         tiles = (span + self.KEYS_PER_TILE - 1) // self.KEYS_PER_TILE + 1
         blocks = n_rows * ((self.n_heads + self.HEADS_PER_BLOCK - 1) // self.HEADS_PER_BLOCK)
         return max(1, min(32, tiles, (2 * self.rt.sm_count) // max(1, blocks)))
-
-    def _per_head(self, a: torch.Tensor, w_kn: torch.Tensor, w_nk: torch.Tensor) -> torch.Tensor:
-        """``a[h] @ w[h]`` for every head, as float32 ``[H, n, m]``.  ``a [H, n, k]`` (any strides with unit stride along k),
-        ``w_kn [H, k, m]`` / ``w_nk [H, m, k]`` the same matrices in both layouts.  bfloat16: one batched library product
-        (32-bit accumulation); 32-bit: the CUDA-core product head by head."""
-        if a.dtype == torch.float32:
-            out = torch.empty((a.shape[0], a.shape[1], w_nk.shape[1]), dtype=torch.float32, device=a.device)
-            for hd in range(a.shape[0]):
-                K.gemm_nt_f32_view(a[hd], w_nk[hd], out[hd])
-            return out
-        return torch.bmm(a, w_kn, out_dtype=torch.float32)

@@ -181,11 +181,15 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory, dtype):
     if dtype == "float32":
         for b, p in enumerate(prompts):
             assert got[b] == P.greedy(cfg, tensors, p, n_new), f"request {b}"
-    else:   # bfloat16 may legitimately part ways at a close call; until then the tokens are the plain ones
-        agree = 0
+    else:
+        # bfloat16 may legitimately part ways with the plain tokens at a close call, and the contexts differ from then on.
+        # Teacher-forced instead: under the plain model, fed our tokens, each of our tokens is the best one up to what
+        # bfloat16 rounding does to logits of this model (a few hundredths of their spread)
         for b, p in enumerate(prompts):
-            agree += sum(1 for x, y in zip(got[b], P.greedy(cfg, tensors, p, n_new)) if x == y)
-        assert agree >= 0.6 * n_new * len(prompts)
+            lg = plain_logits(entry, list(p) + got[b][:-1])[len(p) - 1:]
+            ours = lg.gather(1, torch.tensor(got[b])[:, None])[:, 0]
+            lost = (lg.max(dim=-1).values - ours) / lg.std(dim=-1)
+            assert float(lost.max()) <= 0.25, f"request {b}: token {int(lost.argmax())} loses {float(lost.max()):.3g} spreads to the plain model's best"
     eager = engine(entry, dtype, cuda_graphs=False, max_batch=4)     # graphs and eager steps choose the same tokens
     assert eager.generate_many(prompts, n_new) == got
     chunked = engine(entry, dtype, cuda_graphs=False, max_batch=4, prefill_chunk_tokens=16)
