@@ -139,7 +139,8 @@ class LatentAttention:
             return linear(out, self.w_o, self.rt)
         # few tokens, and everything in 32-bit: kernels of this library (sums in a fixed order, the same whether the step is
         # captured in a graph or not); bfloat16 steps of many tokens: one batched library product over the heads
-        own = h.dtype == torch.float32 or n <= self.rt.small_m_max
+        fits = 4 * (d + 8 * kr) <= 48 * 1024 and 4 * (kr + 8 * dv) <= 48 * 1024     # the kernels' shared memory
+        own = fits and (h.dtype == torch.float32 or n <= self.rt.small_m_max)
         if own:
             q_lat = torch.empty((H, n, kr), dtype=torch.float32, device=dev)
             K.latent_fold_q(q, self.w_uk, q_lat, d)
