@@ -16,8 +16,9 @@
 //                        r_t  = sigmoid(Wa[b] u_t,b + ba) ;  i_t = sigmoid(Wi[b] u_t,b + bi)     (per group b, 32-bit)
 //                        log a_t = -c * r_t * softplus(lam) ;  a_t = exp(log a_t)
 //                        b_t  = sqrt(1 - a_t^2) * i_t * u_t          (1 - a^2 as -expm1(2 log a): no cancellation)
-//                    leaves a_t and b_t [tokens, C] in 32-bit.
-// rglru_scan         S_t = a_t * S_(t-1) + b_t per channel, out_t = T( S_t * gelu_tanh(yproj_t + y_bias) ), then the new
+//                    leaves e_t = a_t - 1 (as expm1(log a_t): a decay of 0.9999 keeps its distance from one, which a
+//                    32-bit a_t would round to one part in 2,000) and b_t, [tokens, C] in 32-bit.
+// rglru_scan         S_t = S_(t-1) + (e_t * S_(t-1) + b_t) per channel, out_t = T( S_t * gelu_tanh(yproj_t + y_bias) ), then the new
 //                    state and the new tail (the last taps-1 inputs) are stored.  Time is walked by eight warps at once,
 //                    each folding its own steps first (see the kernel).
 //
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(G_THREADS) rglru_gates_kernel(
       if (n >= n_tokens) break;
       const float r = 1.f / (1.f + expf(-ar[t])), ig = 1.f / (1.f + expf(-ai[t]));
       const float log_a = -c_mult * r * sp;
-      a_out[(size_t)n * C + c0 + o] = expf(log_a);
+      a_out[(size_t)n * C + c0 + o] = expm1f(log_a);   // a - 1: a decay close to one keeps its distance from one
       b_out[(size_t)n * C + c0 + o] = sqrtf(-expm1f(2.f * log_a)) * ig * u_s[t * nb + o];
     }
   }
@@ -493,7 +494,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 
 // A block takes 32 channels (a lane each) of one sequence and walks time in pieces of SCAN_WARPS * SCAN_SEG steps: every
-// warp folds its own SCAN_SEG steps into one (A, B) pair  S_out = A * S_in + B,  the pairs of the warps before it give its
+// warp folds its own SCAN_SEG steps into one (E, B) pair  S_out = S_in + (E * S_in + B),  the pairs of the warps before it give its
 // S_in, and it walks its steps again for the outputs -- 2 * SCAN_SEG + SCAN_WARPS dependent steps a piece instead of
 // SCAN_WARPS * SCAN_SEG, with every warp's loads in flight at once.
 constexpr int SCAN_WARPS = 8, SCAN_SEG = 16;
@@ -522,22 +523,23 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_kernel(
     for (int i = 0; i < SCAN_SEG; ++i) {
       const int n = first + i;
       const bool ok = on && n < n1;
-      av[i] = ok ? a_in[(size_t)n * C + c] : 1.f;      // steps behind the end change nothing
+      av[i] = ok ? a_in[(size_t)n * C + c] : 0.f;      // a - 1; steps behind the end change nothing
       bv[i] = ok ? b_in[(size_t)n * C + c] : 0.f;
       yv[i] = ok ? to_f32<T>(proj[(size_t)n * ld + y_off + c]) : 0.f;
     }
-    float A = 1.f, B = 0.f;
+    // with e = a - 1:  S <- S + (e S + b);  two steps (E1, B1) then (e, b) compose to  E = E1 + e + E1 e,  B = B1 + (e B1 + b)
+    float E = 0.f, B = 0.f;
 #pragma unroll
-    for (int i = 0; i < SCAN_SEG; ++i) { B = fmaf(av[i], B, bv[i]); A *= av[i]; }
-    As[warp][lane] = A;
+    for (int i = 0; i < SCAN_SEG; ++i) { B += fmaf(av[i], B, bv[i]); E = fmaf(E, av[i], E + av[i]); }
+    As[warp][lane] = E;
     Bs[warp][lane] = B;
     __syncthreads();
     float S = carry[lane];
-    for (int w = 0; w < warp; ++w) S = fmaf(As[w][lane], S, Bs[w][lane]);
+    for (int w = 0; w < warp; ++w) S += fmaf(As[w][lane], S, Bs[w][lane]);
 #pragma unroll
     for (int i = 0; i < SCAN_SEG; ++i) {
       const int n = first + i;
-      S = fmaf(av[i], S, bv[i]);
+      S += fmaf(av[i], S, bv[i]);
       if (on && n < n1) out[(size_t)n * C + c] = from_f32<T>(S * gelu_tanh_f(yv[i] + yb));
     }
     __syncthreads();          // every warp has read the carry
